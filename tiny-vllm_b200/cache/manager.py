@@ -5,7 +5,8 @@ the same need (heads, head size, window) form a *group*; a group has a page
 pool of its own and every request has one block table per group, which all
 runs of the group share.  A group with a window gives a page back as soon as
 every token in it lies before the window of all queries still to come; its
-block-table entry then reads -1.  Every request also holds one *state slot*,
+block-table entry then reads -1 (pages that hold one of the first ``keep_first`` tokens of
+such a group stay: every later query still reads them).  Every request also holds one *state slot*,
 an index into per-run arenas of fixed-size state (empty for dense attention).
 
 A step is a transaction: :meth:`CacheManager.plan` takes the pages that all
@@ -36,6 +37,12 @@ class CacheGroup:
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None          # size of a value, if not head_dim
+    keep_first: int = 0                   # first tokens a window never lets go of
+
+    @property
+    def value_size(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 def ceil_div(a: int, b: int) -> int:
@@ -212,9 +219,15 @@ class CacheManager:
 
     # -------------------------------------------------------------- demand
     def first_needed(self, group: int, next_position: int) -> int:
-        """First key position any query at or after ``next_position`` reads."""
+        """First key position inside the window of any query at or after ``next_position``."""
         window = self.groups[group].window
         return 0 if window is None else max(0, next_position - window + 1)
+
+    def kept_pages(self, group: int) -> int:
+        """Leading pages of a windowed group that are never given back: they hold first tokens
+        that every query keeps seeing."""
+        spec = self.groups[group]
+        return 0 if spec.window is None else ceil_div(max(0, spec.keep_first), self.page_size)
 
     def new_pages(self, request_id, group: int, count: int) -> int:
         """Pages group ``group`` must take to add ``count`` tokens to the request."""
@@ -229,7 +242,7 @@ class CacheManager:
         if window is None:
             return full
         span = window - 1 + max(1, max_step_tokens)
-        return min(full, ceil_div(span, self.page_size) + 1)
+        return min(full, ceil_div(span, self.page_size) + 1 + self.kept_pages(group))
 
     def free_pages(self, group: int) -> int:
         return self.pools[group].free_count
@@ -308,7 +321,8 @@ class CacheManager:
                         self.pools[group].give([p for p in reversed(extra) if p >= 0], entry.request_id)
             for group, table in enumerate(request.tables):
                 first = self.first_needed(group, request.length)
-                passed = [i for i in range(min(len(table), first // size)) if table[i] >= 0]
+                passed = [i for i in range(self.kept_pages(group), min(len(table), first // size))
+                          if table[i] >= 0]
                 if passed:
                     self.pools[group].give([table[i] for i in passed], entry.request_id)
                     for i in passed:

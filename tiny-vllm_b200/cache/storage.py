@@ -1,7 +1,7 @@
 """Device side of the cache: page tensors of every group and state arenas.
 
 Group ``g`` owns two tensors ``[runs_in_group, pages, kv_heads, page_size,
-head_dim]`` (keys, values) in the storage dtype: the keys of one kv head in one
+head_dim]`` (keys, and values, whose last size may differ) in the storage dtype: the keys of one kv head in one
 page are contiguous, so a kernel that serves one kv head reads whole runs of
 memory.  Token ``p`` of a request lies in page ``block_table[p // page_size]``
 at offset ``p % page_size`` of every run of the group (its *slot* is
@@ -22,39 +22,43 @@ from .manager import CacheGroup
 def group_runs(needs: list, cache_from: list) -> tuple[list[CacheGroup], dict[int, tuple[int, int]]]:
     """Groups of equal KV need, and for every run that attends over a cache the
     (group, index inside the group) of the cache it reads."""
-    groups: list[CacheGroup] = []
+    groups: list = []
+    geometries: list[tuple] = []
     members: list[list[int]] = []
     where: dict[int, tuple[int, int]] = {}
     for run, need in enumerate(needs):
         if not isinstance(need, KVNeed) or cache_from[run] is not None:
             continue
-        for g, group in enumerate(groups):
-            if (group.num_kv_heads, group.head_dim, group.window) == (
-                    need.num_kv_heads, need.head_dim, need.window):
+        for g, geometry in enumerate(geometries):
+            if geometry == need.geometry():
                 members[g].append(run)
                 where[run] = (g, len(members[g]) - 1)
                 break
         else:
-            groups.append(CacheGroup((), need.num_kv_heads, need.head_dim, need.window))
+            geometries.append(need.geometry())
+            groups.append(need)
             members.append([run])
             where[run] = (len(groups) - 1, 0)
-    groups = [CacheGroup(tuple(m), g.num_kv_heads, g.head_dim, g.window)
-              for g, m in zip(groups, members)]
+    groups = [CacheGroup(tuple(m), n.num_kv_heads, n.head_dim, n.window,
+                         None if n.value_size == n.head_dim else n.value_size,
+                         n.keep_first if n.window is not None else 0)
+              for n, m in zip(groups, members)]
     for run, source in enumerate(cache_from):
         if source is None:
             continue
         need, theirs = needs[run], needs[source]
         if not isinstance(need, KVNeed) or not isinstance(theirs, KVNeed) or (
-                need.num_kv_heads, need.head_dim) != (theirs.num_kv_heads, theirs.head_dim):
+                need.num_kv_heads, need.head_dim, need.value_size) != (
+                    theirs.num_kv_heads, theirs.head_dim, theirs.value_size):
             raise ValueError(f"run {run} cannot read the cache of run {source}: shapes differ")
-        if need.window != theirs.window:
+        if need.geometry() != theirs.geometry():
             raise ValueError(f"run {run} and run {source} must agree on the window")
         where[run] = where[source]
     return groups, where
 
 
 def bytes_per_page(group: CacheGroup, page_size: int, itemsize: int) -> int:
-    return 2 * len(group.runs) * page_size * group.num_kv_heads * group.head_dim * itemsize
+    return len(group.runs) * page_size * group.num_kv_heads * (group.head_dim + group.value_size) * itemsize
 
 
 class CacheStorage:
@@ -70,9 +74,9 @@ class CacheStorage:
         self.pages_per_group = tuple(pages_per_group)
         self.keys, self.values = [], []
         for group, pages in zip(self.groups, self.pages_per_group):
-            shape = (len(group.runs), pages, group.num_kv_heads, page_size, group.head_dim)
-            self.keys.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.values.append(torch.zeros(shape, dtype=dtype, device=device))
+            shape = (len(group.runs), pages, group.num_kv_heads, page_size)
+            self.keys.append(torch.zeros(shape + (group.head_dim,), dtype=dtype, device=device))
+            self.values.append(torch.zeros(shape + (group.value_size,), dtype=dtype, device=device))
         self.state: dict[int, torch.Tensor] = {}
         for run, need in enumerate(needs):
             if isinstance(need, StateNeed):

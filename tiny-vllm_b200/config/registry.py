@@ -1,6 +1,6 @@
 """The one registry from an architecture's name to its model.
 
-``config.json`` carries ``architectures: ["Qwen3ForCausalLM"]``.  The name is
+``config.json`` carries ``architectures: ["Qwen3ForCausalLM"]`` (or ``architecture: "Gumapel"``).  The name is
 looked up here and gives the typed configuration class of that architecture;
 the configuration turns itself into a :class:`ModelSpec`.  The reference has
 no registry (tinyvllm/models/__init__.py:1-11 only re-exports its one model,
@@ -66,8 +66,11 @@ def parse_model_config(data: Any):
     if not isinstance(data, Mapping):
         raise ConfigError("config.json must hold a JSON object")
     names = data.get("architectures")
+    if names is None and isinstance(data.get("architecture"), str):
+        names = [data["architecture"]]            # some designs name themselves in the singular
     if not isinstance(names, list) or len(names) != 1 or not isinstance(names[0], str):
-        raise ConfigError("config.json must name exactly one entry in 'architectures'")
+        raise ConfigError("config.json must name exactly one entry in 'architectures' "
+                          "(or one name under 'architecture')")
     return lookup_architecture(names[0]).config_class.from_json(data)
 
 

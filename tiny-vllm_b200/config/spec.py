@@ -30,7 +30,7 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None          # None: the layer has no feed-forward (if its block allows)
     norm: PartSpec
 
 

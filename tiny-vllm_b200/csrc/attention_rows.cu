@@ -8,6 +8,11 @@
 // h reads kv head h / (num_q / num_kv) (tinyvllm/kernels/paged_decode.cu:120).
 // Scores, softmax and the output sum are float32 (:302-356, :457-465).
 //
+// Keys and values may differ in size (key_dim, value_dim; both up to 256).  With a window and
+// keep_first > 0 the query also sees the keys 0..keep_first-1 that lie before its window.  An
+// optional gate row g (same layout as the output) multiplies the output by sigmoid(g) before
+// it is rounded and stored.
+//
 // Keys are processed in chunks of ATTN_CHUNK keys that start at absolute
 // multiples of ATTN_CHUNK; every chunk gives a partial (max, sum, output) and the
 // partials are merged in ascending order.  A row's arithmetic is therefore the
@@ -90,7 +95,7 @@ template <typename T>
 __device__ __forceinline__ void attend_chunk(
     Partial& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
     const T* __restrict__ value_cache, const int* __restrict__ table, int first, int last,
-    int kv_head, int num_kv, int head_dim, int page_size, float scale, int lane) {
+    int kv_head, int num_kv, int head_dim, int value_dim, int page_size, float scale, int lane) {
     part.max = -INFINITY;
     part.sum = 0.0f;
 #pragma unroll
@@ -116,16 +121,49 @@ __device__ __forceinline__ void attend_chunk(
         for (int jj = max(0, first - base); jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int64_t sj = __shfl_sync(0xffffffffu, slot, jj);
-            const T* v = value_cache + sj * head_dim;
+            const T* v = value_cache + sj * value_dim;
 #pragma unroll
             for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
                 const int dim = lane + 32 * i;
-                if (dim < head_dim) part.out[i] = __fmaf_rn(pj, to_float<T>(v[dim]), part.out[i]);
+                if (dim < value_dim) part.out[i] = __fmaf_rn(pj, to_float<T>(v[dim]), part.out[i]);
             }
         }
         part.max = new_max;
     }
 }
+
+// Everything of chunk `chunk` that the query at `position` sees: the kept first keys that fall
+// into the chunk (they lie before lo), then the keys of the window.  Both pieces start from an
+// empty partial and are merged in this order, whoever calls.
+template <typename T>
+__device__ __forceinline__ void attend_visible(
+    Partial& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
+    const T* __restrict__ value_cache, const int* __restrict__ table, int chunk, int lo, int kept, int position,
+    int kv_head, int num_kv, int head_dim, int value_dim, int page_size, float scale, int lane) {
+    const int begin = chunk * ATTN_CHUNK, end = begin + ATTN_CHUNK - 1;
+    const int first = max(lo, begin), last = min(position, end);
+    if (kept > begin) {                                   // kept = min(keep_first, lo): keys 0..kept-1
+        attend_chunk<T>(part, q_shared, key_cache, value_cache, table, begin, min(kept - 1, end), kv_head,
+                        num_kv, head_dim, value_dim, page_size, scale, lane);
+        if (first <= last) {
+            Partial more;
+            attend_chunk<T>(more, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv,
+                            head_dim, value_dim, page_size, scale, lane);
+            merge_partial(part, more);
+        }
+        return;
+    }
+    attend_chunk<T>(part, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv, head_dim,
+                    value_dim, page_size, scale, lane);
+}
+
+// Whether the query sees anything of a chunk.
+__device__ __forceinline__ bool chunk_visible(int chunk, int lo, int kept, int position) {
+    const int begin = chunk * ATTN_CHUNK;
+    return begin <= position && (begin + ATTN_CHUNK > lo || kept > begin);
+}
+
+__device__ __forceinline__ float gate_of(float g) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g))); }
 
 // mode rows: grid.x covers (token, head) rows, grid.y = 1, each warp walks all chunks.
 // mode split: grid.y = chunk index; partials go to scratch.
@@ -134,8 +172,9 @@ __global__ void paged_attention_rows_kernel(
     const T* __restrict__ q, int64_t q_token_stride, const T* __restrict__ key_cache,
     const T* __restrict__ value_cache, const int* __restrict__ block_tables, int table_stride,
     const int* __restrict__ token_row, const int* __restrict__ positions, T* __restrict__ out,
+    int64_t out_token_stride, const T* gate, int64_t gate_token_stride,
     float* __restrict__ scratch, int max_chunks, int tokens, int num_q, int num_kv, int head_dim,
-    int page_size, int window, float scale) {
+    int value_dim, int page_size, int window, int keep_first, float scale) {
     __shared__ float q_shared[ATTN_WARPS][256];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * ATTN_WARPS + warp;
@@ -143,15 +182,16 @@ __global__ void paged_attention_rows_kernel(
     const int token = (int)(row / num_q), head = (int)(row % num_q);
     const int position = positions[token];
     const int request = token_row[token];
-    T* out_row = out + row * head_dim;
+    T* out_row = out + (int64_t)token * out_token_stride + (int64_t)head * value_dim;
     if (request < 0 || position < 0) {            // padding row of a captured batch
         if (!SPLIT || blockIdx.y == 0)
-            for (int i = lane; i < head_dim; i += 32) out_row[i] = from_float<T>(0.0f);
+            for (int i = lane; i < value_dim; i += 32) out_row[i] = from_float<T>(0.0f);
         return;
     }
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
-    const int first_chunk = lo / ATTN_CHUNK, last_chunk = position / ATTN_CHUNK;
-    if (SPLIT && ((int)blockIdx.y < first_chunk || (int)blockIdx.y > last_chunk)) return;
+    const int kept = min(keep_first, lo);
+    const int last_chunk = position / ATTN_CHUNK;
+    if (SPLIT && !chunk_visible(blockIdx.y, lo, kept, position)) return;
     const T* q_row = q + (int64_t)token * q_token_stride + (int64_t)head * head_dim;
     for (int i = lane; i < head_dim; i += 32) q_shared[warp][i] = to_float<T>(q_row[i]);
     __syncwarp();
@@ -161,15 +201,14 @@ __global__ void paged_attention_rows_kernel(
     if (SPLIT) {
         const int chunk = blockIdx.y;
         Partial part;
-        attend_chunk<T>(part, q_shared[warp], key_cache, value_cache, table,
-                        max(lo, chunk * ATTN_CHUNK), min(position, chunk * ATTN_CHUNK + ATTN_CHUNK - 1),
-                        kv_head, num_kv, head_dim, page_size, scale, lane);
-        float* dst = scratch + (row * max_chunks + chunk) * (int64_t)(head_dim + 2);
+        attend_visible<T>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
+                          kv_head, num_kv, head_dim, value_dim, page_size, scale, lane);
+        float* dst = scratch + (row * max_chunks + chunk) * (int64_t)(value_dim + 2);
         if (lane == 0) { dst[0] = part.max; dst[1] = part.sum; }
 #pragma unroll
         for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
             const int dim = lane + 32 * i;
-            if (dim < head_dim) dst[2 + dim] = part.out[i];
+            if (dim < value_dim) dst[2 + dim] = part.out[i];
         }
     } else {
         Partial total;
@@ -177,17 +216,22 @@ __global__ void paged_attention_rows_kernel(
         total.sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < ATTN_MAX_DIMS; ++i) total.out[i] = 0.0f;
-        for (int chunk = first_chunk; chunk <= last_chunk; ++chunk) {
+        for (int chunk = 0; chunk <= last_chunk; ++chunk) {
+            if (!chunk_visible(chunk, lo, kept, position)) continue;
             Partial part;
-            attend_chunk<T>(part, q_shared[warp], key_cache, value_cache, table,
-                            max(lo, chunk * ATTN_CHUNK), min(position, chunk * ATTN_CHUNK + ATTN_CHUNK - 1),
-                            kv_head, num_kv, head_dim, page_size, scale, lane);
+            attend_visible<T>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
+                              kv_head, num_kv, head_dim, value_dim, page_size, scale, lane);
             merge_partial(total, part);
         }
+        const T* gate_row = gate ? gate + (int64_t)token * gate_token_stride + (int64_t)head * value_dim : nullptr;
 #pragma unroll
         for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
             const int dim = lane + 32 * i;
-            if (dim < head_dim) out_row[dim] = from_float<T>(__fdiv_rn(total.out[i], total.sum));
+            if (dim < value_dim) {
+                float o = __fdiv_rn(total.out[i], total.sum);
+                if (gate_row) o = __fmul_rn(o, gate_of(to_float<T>(gate_row[dim])));
+                out_row[dim] = from_float<T>(o);
+            }
         }
     }
 }
@@ -196,14 +240,17 @@ template <typename T>
 __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, int max_chunks,
                                             const int* __restrict__ token_row,
                                             const int* __restrict__ positions, T* __restrict__ out,
-                                            int tokens, int num_q, int head_dim, int window) {
+                                            int64_t out_token_stride, const T* gate, int64_t gate_token_stride,
+                                            int tokens, int num_q, int head_dim, int window, int keep_first) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * ATTN_WARPS + warp;
     if (row >= (int64_t)tokens * num_q) return;
-    const int token = (int)(row / num_q);
+    const int token = (int)(row / num_q), head = (int)(row % num_q);
     const int position = positions[token];
     if (token_row[token] < 0 || position < 0) return;     // zeros were written by the first kernel
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
+    const int kept = min(keep_first, lo);
+    T* out_row = out + (int64_t)token * out_token_stride + (int64_t)head * head_dim;
     Partial total;
     total.max = -INFINITY;
     total.sum = 0.0f;
@@ -214,11 +261,12 @@ __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, i
     // and reading on would take the next row's (or leave the buffer).
     const int last_chunk = position / ATTN_CHUNK;
     if (last_chunk >= max_chunks) {
-        T* bad_row = out + row * head_dim;
+        T* bad_row = out_row;
         for (int dim = lane; dim < head_dim; dim += 32) bad_row[dim] = from_float<T>(__int_as_float(0x7fc00000));
         return;
     }
-    for (int chunk = lo / ATTN_CHUNK; chunk <= last_chunk; ++chunk) {
+    for (int chunk = 0; chunk <= last_chunk; ++chunk) {
+        if (!chunk_visible(chunk, lo, kept, position)) continue;
         const float* src = scratch + (row * max_chunks + chunk) * (int64_t)(head_dim + 2);
         Partial part;
         part.max = src[0];
@@ -230,11 +278,15 @@ __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, i
         }
         merge_partial(total, part);
     }
-    T* out_row = out + row * head_dim;
+    const T* gate_row = gate ? gate + (int64_t)token * gate_token_stride + (int64_t)head * head_dim : nullptr;
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
         const int dim = lane + 32 * i;
-        if (dim < head_dim) out_row[dim] = from_float<T>(__fdiv_rn(total.out[i], total.sum));
+        if (dim < head_dim) {
+            float o = __fdiv_rn(total.out[i], total.sum);
+            if (gate_row) o = __fmul_rn(o, gate_of(to_float<T>(gate_row[dim])));
+            out_row[dim] = from_float<T>(o);
+        }
     }
 }
 
@@ -250,14 +302,19 @@ extern "C" long long tvb_attention_rows_scratch_floats(int tokens, int num_q, in
 // tokens * num_q * max_chunks * (head_dim + 2) floats.  The host cannot see the positions:
 // a row whose position needs more chunks than max_chunks is written as NaN (and nothing
 // outside the stated scratch is read or written).
-extern "C" int tvb_attention_rows(const void* q, long long q_token_stride, const void* key_cache,
-                                  const void* value_cache, const int* block_tables, int table_stride,
-                                  const int* token_row, const int* positions, void* out,
-                                  float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
-                                  int head_dim, int page_size, int window, float scale, int dtype,
-                                  void* stream) {
+// The general form: keys `head_dim` and values `value_dim` wide, the first `keep_first` keys seen
+// from behind a window, output rows `out_token_stride` apart, an optional gate with a stride of
+// its own.  Scratch of the split mode: tokens * num_q * max_chunks * (value_dim + 2) floats.
+extern "C" int tvb_attention_rows_general(const void* q, long long q_token_stride, const void* key_cache,
+                                          const void* value_cache, const int* block_tables, int table_stride,
+                                          const int* token_row, const int* positions, void* out,
+                                          long long out_token_stride, const void* gate, long long gate_token_stride,
+                                          float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
+                                          int head_dim, int value_dim, int page_size, int window, int keep_first,
+                                          float scale, int dtype, void* stream) {
     if (tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim > 32 * ATTN_MAX_DIMS || num_q <= 0 || num_kv <= 0 ||
+    if (head_dim <= 0 || head_dim > 32 * ATTN_MAX_DIMS || value_dim <= 0 || value_dim > 32 * ATTN_MAX_DIMS ||
+        num_q <= 0 || num_kv <= 0 || keep_first < 0 ||
         num_q % num_kv || page_size <= 0 || max_chunks < 0 || max_chunks > 65535 ||
         (max_chunks > 0 && !scratch))
         return TVB_BAD_ARGUMENT;
@@ -271,15 +328,18 @@ extern "C" int tvb_attention_rows(const void* q, long long q_token_stride, const
         if (max_chunks > 0) {                                                                       \
             paged_attention_rows_kernel<T, true><<<grid, ATTN_WARPS * 32, 0, s>>>(                  \
                 (const T*)q, q_token_stride, (const T*)key_cache, (const T*)value_cache,            \
-                block_tables, table_stride, token_row, positions, (T*)out, scratch, max_chunks,     \
-                tokens, num_q, num_kv, head_dim, page_size, window, scale);                         \
+                block_tables, table_stride, token_row, positions, (T*)out, out_token_stride,        \
+                (const T*)gate, gate_token_stride, scratch, max_chunks,                             \
+                tokens, num_q, num_kv, head_dim, value_dim, page_size, window, keep_first, scale);  \
             merge_attention_rows_kernel<T><<<(unsigned)blocks, ATTN_WARPS * 32, 0, s>>>(            \
-                scratch, max_chunks, token_row, positions, (T*)out, tokens, num_q, head_dim, window); \
+                scratch, max_chunks, token_row, positions, (T*)out, out_token_stride,               \
+                (const T*)gate, gate_token_stride, tokens, num_q, value_dim, window, keep_first);   \
         } else {                                                                                    \
             paged_attention_rows_kernel<T, false><<<grid, ATTN_WARPS * 32, 0, s>>>(                 \
                 (const T*)q, q_token_stride, (const T*)key_cache, (const T*)value_cache,            \
-                block_tables, table_stride, token_row, positions, (T*)out, scratch, max_chunks,     \
-                tokens, num_q, num_kv, head_dim, page_size, window, scale);                         \
+                block_tables, table_stride, token_row, positions, (T*)out, out_token_stride,        \
+                (const T*)gate, gate_token_stride, scratch, max_chunks,                             \
+                tokens, num_q, num_kv, head_dim, value_dim, page_size, window, keep_first, scale);  \
         }                                                                                           \
     } while (0)
     if (dtype == TVB_F32) LAUNCH_ROWS(float);
@@ -287,6 +347,18 @@ extern "C" int tvb_attention_rows(const void* q, long long q_token_stride, const
     else return TVB_BAD_ARGUMENT;
 #undef LAUNCH_ROWS
     return tvb_last_error();
+}
+
+extern "C" int tvb_attention_rows(const void* q, long long q_token_stride, const void* key_cache,
+                                  const void* value_cache, const int* block_tables, int table_stride,
+                                  const int* token_row, const int* positions, void* out,
+                                  float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
+                                  int head_dim, int page_size, int window, float scale, int dtype,
+                                  void* stream) {
+    return tvb_attention_rows_general(q, q_token_stride, key_cache, value_cache, block_tables, table_stride,
+                                      token_row, positions, out, (long long)num_q * head_dim, nullptr, 0, scratch,
+                                      max_chunks, tokens, num_q, num_kv, head_dim, head_dim, page_size, window, 0,
+                                      scale, dtype, stream);
 }
 
 // ------------------------------------------------ entry point that allocates nothing

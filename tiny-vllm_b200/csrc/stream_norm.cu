@@ -1,0 +1,143 @@
+// A residual stream kept in float32 whatever the storage type, and the kernels around it.
+//
+//   stream_norm   s' = s + (a + b)            (each of s, a, b optional; the sums in float32)
+//                 y  = round_T(s' * rsqrt(mean(s'^2) + eps) * w)     (one rounding, at the end)
+//                 One block per row.  With `gather` only the named rows are produced and the
+//                 stream is not written (the last norm of a model, on the wanted rows).
+//   gated_act     out = round_T(round_T(act(gate)) * up) for gate and up at two offsets of a
+//                 strided row (a packed projection), act = SiLU or the tanh form of GELU
+//   sum_pair      float32 a + b of two tensors of the storage type
+//
+// The statistics, the reciprocal root (a correctly rounded division of a correctly rounded
+// root) and the product with the weight are float32; the order of additions inside a row
+// depends on the width alone, so a row's result does not depend on the batch it is in.
+#include "common.cuh"
+
+template <typename A, typename T, typename W>
+__global__ void stream_norm_kernel(const float* stream_in, const A* add1, const A* add2,
+                                   const W* __restrict__ weight, T* __restrict__ y, float* stream_out,
+                                   const int* __restrict__ gather, int width, float eps) {
+    extern __shared__ float row_values[];
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int out_row = blockIdx.x;
+    const int64_t in_row = gather ? gather[out_row] : out_row;
+    const float* sr = stream_in ? stream_in + in_row * width : nullptr;
+    const A* ar = add1 ? add1 + in_row * width : nullptr;
+    const A* br = add2 ? add2 + in_row * width : nullptr;
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float update = ar ? to_float<A>(ar[i]) : 0.0f;
+        if (br) update = __fadd_rn(update, to_float<A>(br[i]));
+        const float v = sr ? ((ar || br) ? __fadd_rn(sr[i], update) : sr[i]) : update;
+        row_values[i] = v;
+        part = __fmaf_rn(v, v, part);
+    }
+    const float total = block_sum(part, scratch);
+    const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)width), eps)));
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = row_values[i];
+        if (stream_out && !gather) stream_out[(int64_t)out_row * width + i] = v;
+        if (y) y[(int64_t)out_row * width + i] =
+            from_float<T>(__fmul_rn(__fmul_rn(v, inverse_rms), to_float<W>(weight[i])));
+    }
+}
+
+template <typename A, typename T, typename W>
+static int launch_stream_norm(const float* stream_in, const void* add1, const void* add2, const void* weight,
+                              void* y, float* stream_out, const int* gather, int rows, int width, float eps,
+                              int pdl, cudaStream_t s) {
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return TVB_BAD_ARGUMENT;
+    auto kernel = stream_norm_kernel<A, T, W>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : (width >= 128 ? 128 : 32));
+    TvbLaunch launch(dim3(rows), dim3(threads), smem, s, pdl);
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, stream_in, (const A*)add1, (const A*)add2,
+                                       (const W*)weight, (T*)y, stream_out, gather, width, eps);
+    return e == cudaSuccess ? tvb_last_error() : (int)e;
+}
+
+// add_dtype: type of add1 / add2; dtype: type of y; weight_dtype: type of the norm weight.
+extern "C" int tvb_stream_norm(const float* stream_in, const void* add1, const void* add2, int add_dtype,
+                               const void* weight, int weight_dtype, void* y, int dtype, float* stream_out,
+                               const int* gather, int rows, int width, float eps, int pdl, void* stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || (!stream_in && !add1) || (add2 && !add1) || (y && !weight)) return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+#define GO(A, T, W) return launch_stream_norm<A, T, W>(stream_in, add1, add2, weight, y, stream_out, gather, rows, width, eps, pdl, s)
+    if (dtype == TVB_F32 && weight_dtype == TVB_F32 && add_dtype == TVB_F32) GO(float, float, float);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_BF16 && add_dtype == TVB_F32) GO(float, bf16, bf16);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_BF16 && add_dtype == TVB_BF16) GO(bf16, bf16, bf16);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_F32 && add_dtype == TVB_F32) GO(float, bf16, float);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_F32 && add_dtype == TVB_BF16) GO(bf16, bf16, float);
+#undef GO
+    return TVB_BAD_ARGUMENT;
+}
+
+// ------------------------------------------------------------ act(gate) * up
+#define TVB_ACT_SILU 0
+#define TVB_ACT_GELU_TANH 1
+
+template <int ACT> __device__ __forceinline__ float activate(float z) {
+    if (ACT == TVB_ACT_SILU) return __fdiv_rn(z, __fadd_rn(1.0f, expf(-z)));
+    // 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+    const float inner = __fmul_rn(0.7978845608028654f, __fmaf_rn(__fmul_rn(0.044715f, z), __fmul_rn(z, z), z));
+    return __fmul_rn(__fmul_rn(0.5f, z), __fadd_rn(1.0f, tanhf(inner)));
+}
+
+template <typename T, int ACT>
+__global__ void gated_act_kernel(const T* in, int64_t in_stride, int gate_at, int up_at, T* __restrict__ out,
+                                 int64_t out_stride, int inter) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t row = blockIdx.y;
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= inter) return;
+    const T* src = in + row * in_stride;
+    const float gate = to_float<T>(src[gate_at + col]);
+    const float up = to_float<T>(src[up_at + col]);
+    out[row * out_stride + col] = from_float<T>(__fmul_rn(round_to<T>(activate<ACT>(gate)), up));
+}
+
+extern "C" int tvb_gated_act(const void* in, long long in_stride, int gate_at, int up_at, void* out,
+                             long long out_stride, int rows, int inter, int act, int dtype, void* stream) {
+    if (rows <= 0) return 0;
+    if (inter <= 0 || (act != TVB_ACT_SILU && act != TVB_ACT_GELU_TANH)) return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int first = 0; first < rows; first += 65535) {
+        const int count = rows - first < 65535 ? rows - first : 65535;
+        dim3 grid((inter + 255) / 256, count);
+#define GO(T, ACT)                                                                                   \
+    gated_act_kernel<T, ACT><<<grid, 256, 0, s>>>((const T*)in + (int64_t)first * in_stride, in_stride, \
+                                                  gate_at, up_at, (T*)out + (int64_t)first * out_stride, out_stride, inter)
+        if (dtype == TVB_F32 && act == TVB_ACT_SILU) GO(float, TVB_ACT_SILU);
+        else if (dtype == TVB_F32) GO(float, TVB_ACT_GELU_TANH);
+        else if (dtype == TVB_BF16 && act == TVB_ACT_SILU) GO(bf16, TVB_ACT_SILU);
+        else if (dtype == TVB_BF16) GO(bf16, TVB_ACT_GELU_TANH);
+        else return TVB_BAD_ARGUMENT;
+#undef GO
+    }
+    return tvb_last_error();
+}
+
+// ------------------------------------------------------------- float32 a + b
+template <typename T>
+__global__ void sum_pair_kernel(const T* a, const T* b, float* __restrict__ out, int64_t count) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = __fadd_rn(to_float<T>(a[i]), to_float<T>(b[i]));
+}
+
+extern "C" int tvb_sum_pair(const void* a, const void* b, float* out, long long count, int dtype, void* stream) {
+    if (count <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (dtype == TVB_F32) sum_pair_kernel<float><<<blocks, 256, 0, s>>>((const float*)a, (const float*)b, out, count);
+    else if (dtype == TVB_BF16) sum_pair_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)a, (const bf16*)b, out, count);
+    else return TVB_BAD_ARGUMENT;
+    return tvb_last_error();
+}

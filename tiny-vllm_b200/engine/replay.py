@@ -35,7 +35,8 @@ def build_runner(model_dir, dtype: str, max_tokens: int, *, page_size: int = PAG
     config = read_model_config(model_dir)
     model = Model(config.to_spec(), device=device, dtype=torch_dtype).load(model_dir)
     pages = -(-max_tokens // page_size)
-    return StepRunner(model, page_size=page_size, num_pages=pages, max_requests=MAX_LIVE_REQUESTS)
+    return StepRunner(model, page_size=page_size, num_pages=pages, max_requests=MAX_LIVE_REQUESTS,
+                      max_model_len=pages * page_size)
 
 
 def replay(runner: StepRunner, lines, out_dir: Path, *, report=print) -> None:

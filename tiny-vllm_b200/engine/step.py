@@ -17,7 +17,7 @@ entry, not only its last token; there is no per-request loop on the host.
 from __future__ import annotations
 
 import logging
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Sequence
 
 import numpy as np
@@ -84,6 +84,7 @@ class StepContext:
     signature: tuple = ()                # sizes and flags that fix the step's launches (two steps with the
                                          # same signature differ in the contents of their tensors only)
     arena: torch.Tensor | None = None    # the int32 tensor all the fields above are views of
+    shared: dict = field(default_factory=dict)   # what a layer of this step hands on to later layers
 
     def writes_cache(self, run: int) -> bool:
         return self.cache_sources[run] is None

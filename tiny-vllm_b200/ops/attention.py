@@ -249,3 +249,50 @@ def mixer_attention(ctx, mixer, qkv: torch.Tensor, run: int) -> torch.Tensor:
     return kernels.attention_rows(
         qkv, qkv.shape[1], keys, values, ctx.block_tables[group], ctx.token_row, ctx.positions,
         **heads, window=mixer.window, scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks)
+
+
+def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, out: torch.Tensor) -> None:
+    """The attention of a mixer whose sizes and steps are parameters (``parts.WindowedAttention``):
+    from its columns of a projection [tokens, columns] (q heads from column ``at``, then k heads, v
+    heads and, if it has one, the gate) to the gated, concatenated heads in ``out`` [tokens,
+    heads * value_dim] (rows may be strided); writes the step's keys and values.
+
+    q and k are prepared in float32 (norm over the head, rotation by position * frequency), the
+    values blended with those the step's first blending layer handed on, keys and values go to
+    their pages; then every query attends its window and the first tokens the window keeps,
+    with float32 scores, weights and sums."""
+    keys, values = ctx.storage.kv_of(run)
+    group = ctx.storage.group_of(run)
+    writes = ctx.writes_cache(run)
+    q_at, k_at = at, at + mixer.q_cols
+    v_at = k_at + mixer.k_cols
+    g_at = v_at + mixer.v_cols
+    v_here = projected[:, v_at:v_at + mixer.v_cols]
+    v_first = None
+    if mixer.value_mix == "first":
+        ctx.shared[mixer.value_mix_key] = v_here
+    elif mixer.value_mix == "blend":
+        v_first = ctx.shared.get(mixer.value_mix_key)
+        if v_first is None or v_first.shape != v_here.shape:
+            raise kernels.KernelError("a layer blends its values with those of an earlier layer of the same "
+                                      "shape, which has to run before it in the same step")
+    position = mixer.position
+    kernels.qkv_prepare(
+        projected, q_at=q_at, k_at=k_at, v_at=v_at, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads,
+        key_dim=mixer.key_dim, value_dim=mixer.value_dim, positions=ctx.positions, norm=mixer.qk_norm,
+        q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps,
+        inv_freq=None if position is None else position.inv_freq,
+        rot_dims=0 if position is None else position.rot_dims,
+        pairing="interleaved" if position is None else position.pairing,
+        slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values,
+        v_first=v_first, blend=mixer.vmix if v_first is not None else None)
+    gate = projected[:, g_at:g_at + mixer.out_cols] if mixer.gate else None
+    scratch = None
+    if ctx.split_chunks > 0:
+        scratch = ctx.workspace(kernels.attention_rows_scratch_floats(
+            ctx.num_tokens, mixer.num_heads, mixer.value_dim, ctx.split_chunks))
+    kernels.attention_rows(
+        projected[:, q_at:q_at + mixer.q_cols], projected.stride(0), keys, values, ctx.block_tables[group],
+        ctx.token_row, ctx.positions, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.key_dim,
+        value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale,
+        gate=gate, out=out, scratch=scratch, max_chunks=ctx.split_chunks)

@@ -287,6 +287,7 @@ def attention_chunk_keys() -> int:
 
 
 def attention_rows_scratch_floats(tokens: int, num_q: int, head_dim: int, max_chunks: int) -> int:
+    """``head_dim``: the size of a value."""
     return tokens * num_q * max_chunks * (head_dim + 2)
 
 
@@ -294,42 +295,206 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
                    value_cache: torch.Tensor, block_tables: torch.Tensor, token_row: torch.Tensor,
                    positions: torch.Tensor, *, num_q: int, num_kv: int, head_dim: int,
                    window: int | None, scale: float, out: torch.Tensor | None = None,
-                   scratch: torch.Tensor | None = None, max_chunks: int = 0) -> torch.Tensor:
+                   scratch: torch.Tensor | None = None, max_chunks: int = 0,
+                   value_dim: int | None = None, keep_first: int = 0,
+                   gate: torch.Tensor | None = None) -> torch.Tensor:
     """Paged causal attention, one warp per (token, head).
 
     ``q`` holds the query heads of token t at ``t * q_token_stride`` elements
     (the packed projection serves as it is).  ``max_chunks > 0`` spreads the
     chunks of every row over the grid and needs ``scratch`` (float32, at least
-    :func:`attention_rows_scratch_floats` long); 0 walks them in one warp."""
-    _need_cuda(q, key_cache, value_cache, block_tables, token_row, positions, scratch)
+    :func:`attention_rows_scratch_floats` long); 0 walks them in one warp.
+    ``value_dim``: size of a value if it is not ``head_dim``; ``keep_first``: with a window, the
+    first so many keys stay visible; ``gate`` [tokens, num_q * value_dim] (rows may be strided):
+    the output is multiplied by sigmoid(gate); ``out`` may have strided rows too."""
+    _need_cuda(q, key_cache, value_cache, block_tables, token_row, positions, scratch, gate)
     tokens = positions.shape[0]
-    if head_dim > 256 or num_q % num_kv:
+    value_dim = head_dim if value_dim is None else value_dim
+    if head_dim > 256 or value_dim > 256 or num_q % num_kv:
         raise KernelError(f"attention_rows takes head sizes up to 256 and whole groups "
                           f"(head_dim {head_dim}, {num_q} / {num_kv} heads)")
     if key_cache.dim() != 4 or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, head_dim) or \
-            value_cache.shape != key_cache.shape or key_cache.dtype != q.dtype or \
+            value_cache.shape != key_cache.shape[:3] + (value_dim,) or key_cache.dtype != q.dtype or \
             not key_cache.is_contiguous() or not value_cache.is_contiguous():
         raise KernelError("attention_rows: caches must be contiguous [pages, num_kv, page_size, head_dim]")
+    for name, t in (("out", out), ("gate", gate)):
+        if t is not None and (t.dim() != 2 or t.shape != (tokens, num_q * value_dim) or t.stride(1) != 1
+                              or t.dtype != q.dtype):
+            raise KernelError(f"attention_rows: {name} must be [tokens, num_q * value_dim] of the dtype of q "
+                              "with contiguous rows")
     for name, t in (("block_tables", block_tables), ("token_row", token_row), ("positions", positions)):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError(f"attention_rows: {name} must be contiguous int32")
     if block_tables.dim() != 2 or token_row.shape != (tokens,):
         raise KernelError("attention_rows: block_tables [requests, blocks], token_row [tokens]")
     if out is None:
-        out = torch.empty((tokens, num_q * head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((tokens, num_q * value_dim), dtype=q.dtype, device=q.device)
     if max_chunks > 0:
-        need = attention_rows_scratch_floats(tokens, num_q, head_dim, max_chunks)
+        need = attention_rows_scratch_floats(tokens, num_q, value_dim, max_chunks)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention_rows: split mode needs {need} float32 of scratch")
-    fn = _fn("attention_rows", "tvb_attention_rows",
+    fn = _fn("attention_rows", "tvb_attention_rows_general",
              [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+              c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_int, c_int, c_float, c_int, c_void_p])
     _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_cache.data_ptr(),
               block_tables.data_ptr(), block_tables.shape[1], token_row.data_ptr(),
-              positions.data_ptr(), out.data_ptr(), _ptr(scratch), max_chunks, tokens, num_q, num_kv,
-              head_dim, key_cache.shape[2], window or 0, scale, dtype_tag(q.dtype), _stream()),
+              positions.data_ptr(), out.data_ptr(), out.stride(0), _ptr(gate),
+              0 if gate is None else gate.stride(0), _ptr(scratch), max_chunks, tokens, num_q, num_kv,
+              head_dim, value_dim, key_cache.shape[2], window or 0, keep_first if window else 0, scale,
+              dtype_tag(q.dtype), _stream()),
            "attention_rows", 2 if max_chunks > 0 else 1)
     return out
+
+
+
+# ------------------------------------------------ a float32 residual stream
+def stream_norm(stream: torch.Tensor | None, weight: torch.Tensor | None, eps: float, *,
+                add: torch.Tensor | None = None, add2: torch.Tensor | None = None,
+                rows: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+                want_output: bool = True):
+    """The pre-norm of a model whose residual stream is float32 whatever its storage type.
+
+    s' = stream + (add + add2) in float32 (any of the three may be missing, not all), written back
+    into ``stream`` (a new tensor without one); y = s' * rsqrt(mean(s'^2) + eps) * weight, rounded
+    once, in ``out_dtype``.  Returns (y, s').  With ``rows`` (int32) only those rows of y are
+    produced and nothing is written back: (y, None).  ``want_output=False``: only the sum."""
+    _need_cuda(stream, weight, add, add2, rows)
+    first = stream if stream is not None else add
+    if first is None or first.dim() != 2 or not first.is_contiguous():
+        raise KernelError("stream_norm wants a contiguous [tokens, width] stream or addend")
+    tokens, width = first.shape
+    if stream is not None and stream.dtype != torch.float32:
+        raise KernelError("stream_norm: the stream is float32")
+    if add2 is not None and add is None:
+        raise KernelError("stream_norm: a second addend needs a first")
+    for t in (add, add2):
+        if t is not None and (t.shape != (tokens, width) or not t.is_contiguous() or t.dtype != add.dtype):
+            raise KernelError("stream_norm: addends must match the stream's shape and each other's dtype")
+    if width * 4 > 200 * 1024:
+        raise KernelError(f"stream_norm: width {width} is larger than a row buffer of shared memory holds")
+    if want_output and (weight is None or weight.shape != (width,)):
+        raise KernelError("stream_norm wants a weight [width]")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("stream_norm: rows must be int32")
+    count = tokens if rows is None else rows.shape[0]
+    out_dtype = out_dtype or (add.dtype if add is not None and add.dtype != torch.float32 else
+                              weight.dtype if weight is not None else torch.float32)
+    y = torch.empty((count, width), dtype=out_dtype, device=first.device) if want_output else None
+    stream_out = None
+    if rows is None:
+        stream_out = stream if stream is not None else torch.empty((tokens, width), dtype=torch.float32,
+                                                                   device=first.device)
+    fn = _fn("stream_norm", "tvb_stream_norm",
+             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_ptr(stream), _ptr(add), _ptr(add2), dtype_tag(add.dtype) if add is not None else F32,
+              _ptr(weight) if want_output else None,
+              dtype_tag(weight.dtype) if weight is not None else dtype_tag(out_dtype), _ptr(y),
+              dtype_tag(out_dtype), _ptr(stream_out), _ptr(rows), count, width, eps, 0, _stream()), "stream_norm")
+    return y, stream_out
+
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+
+
+def gated_act(packed: torch.Tensor, gate_at: int, up_at: int, inter: int, activation: str, *,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """round(round(act(gate)) * up) where gate and up are the ``inter`` columns of ``packed``
+    [tokens, any] from ``gate_at`` and ``up_at`` on; ``out`` [tokens, inter] may have strided rows."""
+    _need_cuda(packed, out)
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gated_act knows {', '.join(ACTIVATIONS)}, not {activation!r}")
+    if packed.dim() != 2 or packed.stride(1) != 1 or min(gate_at, up_at) < 0 or \
+            max(gate_at, up_at) + inter > packed.shape[1]:
+        raise KernelError("gated_act wants [tokens, columns] with contiguous rows that hold gate and up")
+    tokens = packed.shape[0]
+    if out is None:
+        out = torch.empty((tokens, inter), dtype=packed.dtype, device=packed.device)
+    elif out.shape != (tokens, inter) or out.dtype != packed.dtype or out.stride(1) != 1:
+        raise KernelError("gated_act: out must be [tokens, inter] of the input's dtype with contiguous rows")
+    fn = _fn("stream_norm", "tvb_gated_act",
+             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(packed.data_ptr(), packed.stride(0), gate_at, up_at, out.data_ptr(), out.stride(0), tokens, inter,
+              ACTIVATIONS[activation], dtype_tag(packed.dtype), _stream()), "gated_act")
+    return out
+
+
+def sum_pair(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """float32 a + b of two contiguous tensors of one shape and dtype."""
+    _need_cuda(a, b)
+    if a.shape != b.shape or a.dtype != b.dtype or not a.is_contiguous() or not b.is_contiguous():
+        raise KernelError("sum_pair wants two contiguous tensors of one shape and dtype")
+    out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    fn = _fn("stream_norm", "tvb_sum_pair", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+    _check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), dtype_tag(a.dtype), _stream()), "sum_pair")
+    return out
+
+
+# ------------------- q/k norm, rotation, value blend and cache write with every size a parameter
+NORM_MODES = {None: 0, "unit": 1, "weight": 2}
+PAIRINGS = {"interleaved": 0, "half_split": 1}
+
+
+def qkv_prepare(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, num_q: int, num_kv: int,
+                key_dim: int, value_dim: int, positions: torch.Tensor, norm: str | None = None,
+                q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None, eps: float = 0.0,
+                inv_freq: torch.Tensor | None = None, rot_dims: int = 0, pairing: str = "interleaved",
+                slots: torch.Tensor | None, key_cache: torch.Tensor | None, value_cache: torch.Tensor | None,
+                v_first: torch.Tensor | None = None, blend: torch.Tensor | None = None) -> None:
+    """In place on a packed projection [tokens, columns] that holds the q heads from column
+    ``q_at``, the k heads from ``k_at`` and the v heads from ``v_at``: q and k heads are normalised
+    over the head (``norm`` None, "unit" or "weight") and rotated (``inv_freq`` float32
+    [rot_dims / 2]; the angle is position * inv_freq in float32), q where it stands, k into
+    ``key_cache`` [pages, num_kv, page, key_dim] at ``slots``; v heads go to ``value_cache``
+    [pages, num_kv, page, value_dim], blended as (1 - blend) v + blend v_first when ``v_first``
+    [tokens, num_kv * value_dim] (rows may be strided) and the one-element ``blend`` are given."""
+    _need_cuda(proj, positions, q_weight, k_weight, inv_freq, slots, key_cache, value_cache, v_first, blend)
+    tokens = proj.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("qkv_prepare: the projection must be [tokens, columns] with contiguous rows")
+    if min(q_at, k_at, v_at) < 0 or max(q_at + num_q * key_dim, k_at + num_kv * key_dim,
+                                        v_at + num_kv * value_dim) > proj.shape[1]:
+        raise KernelError("qkv_prepare: the heads do not fit the projection's rows")
+    if key_dim % 2 or key_dim > 256 or value_dim > 256:
+        raise KernelError(f"qkv_prepare takes even key sizes and sizes up to 256, not {key_dim} / {value_dim}")
+    if positions.dtype != torch.int32 or positions.shape != (tokens,):
+        raise KernelError("qkv_prepare: positions must be int32 [tokens]")
+    if norm not in NORM_MODES or pairing not in PAIRINGS:
+        raise KernelError(f"qkv_prepare: norm {norm!r} or pairing {pairing!r} is not known")
+    weight_tag = dtype_tag(proj.dtype)
+    if norm == "weight":
+        if q_weight is None or k_weight is None or q_weight.shape != (key_dim,) or k_weight.shape != (key_dim,) \
+                or q_weight.dtype != k_weight.dtype:
+            raise KernelError("qkv_prepare: norm weights must be [key_dim] of one dtype")
+        weight_tag = dtype_tag(q_weight.dtype)
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.shape != (rot_dims // 2,)
+                                 or rot_dims % 2 or not 0 < rot_dims <= key_dim or not inv_freq.is_contiguous()):
+        raise KernelError("qkv_prepare: inv_freq must be float32 [rot_dims / 2] with rot_dims <= key_dim")
+    if slots is not None:
+        if (slots.dtype != torch.int32 or slots.shape != (tokens,) or key_cache is None or value_cache is None
+                or key_cache.dim() != 4 or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, key_dim)
+                or value_cache.shape != key_cache.shape[:3] + (value_dim,) or key_cache.dtype != proj.dtype
+                or value_cache.dtype != proj.dtype or not key_cache.is_contiguous()
+                or not value_cache.is_contiguous()):
+            raise KernelError("qkv_prepare: slots int32 [tokens]; caches contiguous [pages, num_kv, page_size, "
+                              "key_dim / value_dim] of the projection's dtype")
+    if v_first is not None:
+        if (blend is None or blend.numel() != 1 or blend.dtype != proj.dtype or v_first.dtype != proj.dtype
+                or v_first.shape != (tokens, num_kv * value_dim) or v_first.stride(1) != 1):
+            raise KernelError("qkv_prepare: v_first [tokens, num_kv * value_dim] and a one-element blend, both "
+                              "of the projection's dtype")
+    fn = _fn("qkv_prepare", "tvb_qkv_prepare",
+             [c_void_p, c_longlong] + [c_int] * 8 + [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int,
+                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                    c_longlong, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(proj.data_ptr(), proj.stride(0), q_at, k_at, v_at, num_q, num_kv, key_dim, value_dim,
+              NORM_MODES[norm], _ptr(q_weight), _ptr(k_weight), weight_tag, eps, _ptr(inv_freq), rot_dims,
+              PAIRINGS[pairing], positions.data_ptr(), _ptr(slots), _ptr(key_cache), _ptr(value_cache),
+              key_cache.shape[2] if slots is not None else 0, _ptr(v_first),
+              0 if v_first is None else v_first.stride(0), _ptr(blend), tokens, dtype_tag(proj.dtype),
+              _stream()), "qkv_prepare")
 
 
 # ----------------------------------------------------------------------- GEMM

@@ -54,11 +54,15 @@ import torch
 
 @dataclass(frozen=True)
 class ParamSource:
-    """One checkpoint tensor and the rows of the destination it fills."""
+    """One checkpoint tensor and the rows of the destination it fills; with ``cols`` it fills
+    only the columns ``col_start .. col_start + cols`` of those rows (weights packed side by
+    side along their input axis)."""
 
     name: str
     row_start: int
     rows: int
+    col_start: int = 0
+    cols: int | None = None
 
 
 @dataclass(frozen=True)
@@ -68,8 +72,9 @@ class ParamSpec:
     ``sources`` lists the checkpoint tensors that are packed along the first
     dimension.  ``role``: "matrix" and "table" tensors take the storage dtype;
     a "vector" that the file stores in 32-bit stays in 32-bit; "integer"
-    tensors become int32.  ``init`` is the law of the random-weights mode:
-    "normal" draws N(0, 0.02), "around_one" draws 1 + U(-0.1, 0.1).
+    tensors become int32; a "scalar" is stored without a shape and bound as one element.
+    ``init`` is the law of the random-weights mode: "normal" draws N(0, 0.02), "around_one"
+    draws 1 + U(-0.1, 0.1), "unit_interval" draws U(0, 1).
     """
 
     attr: str
@@ -84,6 +89,19 @@ class ParamSpec:
         return ParamSpec(attr, shape, (ParamSource(name, 0, shape[0]),), role, init)
 
     @staticmethod
+    def scalar(attr: str, name: str, *, init: str = "unit_interval") -> "ParamSpec":
+        return ParamSpec(attr, (1,), (ParamSource(name, 0, 1),), "scalar", init)
+
+    @staticmethod
+    def side_by_side(attr: str, rows: int, names_cols: list[tuple[str, int]]) -> "ParamSpec":
+        """[rows, sum of cols]: every source fills its own columns of all rows."""
+        sources, start = [], 0
+        for name, cols in names_cols:
+            sources.append(ParamSource(name, 0, rows, start, cols))
+            start += cols
+        return ParamSpec(attr, (rows, start), tuple(sources))
+
+    @staticmethod
     def packed(attr: str, names_rows: list[tuple[str, int]], cols: int) -> "ParamSpec":
         sources, start = [], 0
         for name, rows in names_rows:
@@ -94,11 +112,24 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class KVNeed:
-    """A growing cache of keys and values, ``window`` keys long if given."""
+    """A growing cache of keys and values, ``window`` keys long if given.  ``value_dim``: the size
+    of a value where it differs from that of a key (``head_dim``).  ``keep_first``: a windowed
+    cache never lets go of its first so many tokens (queries keep seeing them)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+    keep_first: int = 0
+
+    @property
+    def value_size(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
+
+    def geometry(self) -> tuple:
+        """What two runs must agree on to share pages and block tables."""
+        return (self.num_kv_heads, self.head_dim, self.value_size, self.window,
+                self.keep_first if self.window is not None else 0)
 
 
 @dataclass(frozen=True)

@@ -8,7 +8,10 @@ model's final norm) adds it (tinyvllm/models/qwen3.py:386-412).
 
 from __future__ import annotations
 
-from .base import Block, BuildContext
+import torch
+
+from ..ops import kernels, linear
+from .base import Block, BuildContext, ParamSpec
 from .registry import register_part
 
 
@@ -48,4 +51,69 @@ def _normed(norm, hidden, residual):
     return norm.add(hidden, residual)
 
 
+class ParallelResidualBlock(Block):
+    """One norm, and mixer and feed-forward side by side: with h = norm(x), x <- x + (mixer(h) +
+    feed_forward(h)).  The residual stream x is float32 whatever the storage type; the sum of the
+    two outputs is float32 and is added to the stream by the next norm (or the model's last one).
+
+    Parts that can be a block's guests (``input_rows``, ``output_cols``, ``between``) share two
+    products: all input projections are the rows of one weight [sum of rows, width], all output
+    projections stand side by side in one weight [width, sum of columns], whose product with the
+    concatenated inner activations is the float32 sum mixer(h) + feed_forward(h) itself.  Parts
+    that cannot are run through their ``forward`` and their outputs are added.  A layer may have
+    no feed-forward."""
+
+    def __init__(self, ctx: BuildContext, *, mixer, feed_forward, norm, norm_name: str, mixer_name: str,
+                 feed_forward_name: str, share_products: bool = True) -> None:
+        self.norm = ctx.build("norm", norm, ctx.child(norm_name))
+        self.width = norm.params["width"]
+        self.shared = share_products
+        hosted = {"hosted": True} if share_products else {}
+        self.mixer = ctx.build("mixer", mixer.with_params(**hosted), ctx.child(mixer_name))
+        self.feed_forward = None
+        if feed_forward is not None:
+            self.feed_forward = ctx.build("feed_forward", feed_forward.with_params(**hosted),
+                                          ctx.child(feed_forward_name))
+        self.guests = [part for part in (self.mixer, self.feed_forward) if part is not None]
+        if share_products and not all(hasattr(part, "between") for part in self.guests):
+            raise ValueError("a block shares its products only among parts that can be its guests")
+        self.in_weight = self.out_weight = None
+
+    def children(self):
+        return [self.norm] + self.guests
+
+    def param_specs(self):
+        if not self.shared:
+            return []
+        rows = [pair for part in self.guests for pair in part.input_rows()]
+        cols = [part.output_cols() for part in self.guests]
+        return [ParamSpec.packed("in_weight", rows, self.width),
+                ParamSpec.side_by_side("out_weight", self.width, cols)]
+
+    def streamed_weights(self):
+        return [self.in_weight, self.out_weight] if self.shared else []
+
+    def forward(self, hidden, residual, ctx, run: int):
+        x, residual = self.norm.add(hidden, residual)
+        if not self.shared:
+            update = self.mixer.forward(x, ctx, run)
+            if self.feed_forward is not None:
+                update = kernels.sum_pair(update, self.feed_forward.forward(x, ctx))
+            return update, residual
+        projected = linear(x, self.in_weight)
+        inner = torch.empty((x.shape[0], self.out_weight.shape[1]), dtype=x.dtype, device=x.device)
+        at_in = at_out = 0
+        for part in self.guests:
+            columns = part.output_cols()[1]
+            out = inner[:, at_out:at_out + columns]
+            if part is self.mixer:
+                part.between(projected, at_in, ctx, out, run)
+            else:
+                part.between(projected, at_in, ctx, out)
+            at_in += sum(rows for _, rows in part.input_rows())
+            at_out += columns
+        return linear(inner, self.out_weight, out_dtype=torch.float32), residual
+
+
 register_part("block", "prenorm_residual", PreNormResidualBlock)
+register_part("block", "parallel_residual", ParallelResidualBlock)

@@ -7,6 +7,8 @@ sum with the residual stream and returns it as the new stream
 
 from __future__ import annotations
 
+import torch
+
 from ..ops import kernels
 from .base import BuildContext, ParamSpec, Part
 from .registry import register_part
@@ -37,4 +39,43 @@ class RMSNorm(Part):
         return kernels.rms_norm(x, self.weight, self.eps, residual=residual, rows=rows)
 
 
+class StreamRMSNorm(Part):
+    """RMSNorm in front of a float32 residual stream: y = s * rsqrt(mean(s^2) + eps) * weight with
+    statistics, scaling and the product with the weight in float32 and one rounding, to the
+    storage type, at the end.  ``add`` first forms s = residual + x in float32 (x may be of the
+    storage type or float32) and keeps s, in place, as the new stream.  The stream is float32
+    also where activations and weights are bfloat16."""
+
+    def __init__(self, ctx: BuildContext, *, width: int, eps: float, name: str | None = None) -> None:
+        self.width = width
+        self.eps = float(eps)
+        self.name = name if name is not None else f"{ctx.prefix}.weight"
+        self.out_dtype = ctx.dtype
+        self.weight = None
+
+    def param_specs(self):
+        return [ParamSpec.single("weight", self.name, (self.width,), role="vector", init="around_one")]
+
+    def forward(self, x):
+        """norm(x) for a float32 stream or for activations that start one."""
+        if x.dtype == torch.float32:
+            return kernels.stream_norm(x, self.weight, self.eps, out_dtype=self.out_dtype)[0]
+        return kernels.stream_norm(None, self.weight, self.eps, add=x, out_dtype=self.out_dtype)[0]
+
+    def add(self, x, residual):
+        """(norm(residual + x), residual + x); without a residual x starts the stream, without x
+        the stream holds the sum already."""
+        if residual is not None and residual.dtype != torch.float32:
+            raise kernels.KernelError("this norm keeps its residual stream in float32")
+        return kernels.stream_norm(residual, self.weight, self.eps, add=x, out_dtype=self.out_dtype)
+
+    def add_rows(self, x, residual, rows):
+        """norm(residual + x) on the rows named by ``rows`` only; nothing is written back."""
+        if residual is None and x.dtype == torch.float32:
+            x, residual = None, x
+        return kernels.stream_norm(residual, self.weight, self.eps, add=x, rows=rows,
+                                   out_dtype=self.out_dtype)[0]
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "rms_norm_stream32", StreamRMSNorm)

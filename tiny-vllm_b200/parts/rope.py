@@ -47,4 +47,30 @@ class RopeHalfSplit(Part):
         self.cos, self.sin = _TABLES[key]
 
 
+class RopeInterleaved(Part):
+    """Rotary encoding with neighbouring dimensions paired: (2i, 2i + 1) of the first ``dims``
+    dimensions of a head turn by position * base^(-2i / dims); the rest of the head passes.  No
+    tables: the kernel that prepares q and k multiplies the position with ``inv_freq`` (float32)
+    and takes sine and cosine itself, so there is no limit on positions."""
+
+    pairing = "interleaved"
+
+    def __init__(self, ctx: BuildContext, *, dims: int, base: float) -> None:
+        if dims <= 0 or dims % 2:
+            raise ValueError("rotary encoding needs an even, positive number of dimensions")
+        self.rot_dims = dims
+        self.base = float(base)
+        self.device = ctx.device
+        self.inv_freq = None
+
+    def inverse_frequencies(self) -> torch.Tensor:
+        """base^(-2i / dims), evaluated in double precision and rounded to float32 once."""
+        exponent = torch.arange(0, self.rot_dims, 2, dtype=torch.float64) / self.rot_dims
+        return (self.base ** -exponent).to(torch.float32)
+
+    def finalize(self) -> None:
+        self.inv_freq = self.inverse_frequencies().to(self.device)
+
+
 register_part("position", "rope_half_split", RopeHalfSplit)
+register_part("position", "rope_interleaved", RopeInterleaved)

@@ -69,6 +69,15 @@ def storage_dtype_of(spec: ParamSpec, stored: torch.dtype, dtype: torch.dtype) -
     return dtype
 
 
+def source_shape(spec: ParamSpec, source) -> tuple[int, ...]:
+    """Shape of the checkpoint tensor ``source`` names."""
+    if spec.role == "scalar":
+        return ()
+    if source.cols is not None:
+        return (source.rows, source.cols) + tuple(spec.shape[2:])
+    return (source.rows,) + tuple(spec.shape[1:])
+
+
 def _routes(targets: Iterable[tuple[Part, ParamSpec]]):
     routes = {}
     for part, spec in targets:
@@ -108,7 +117,7 @@ def bind_tensors(targets, named_tensors, *, dtype, device, folder="<memory>",
                 unexpected.append(name)
             continue
         part, spec, source = route
-        want = (source.rows,) + tuple(spec.shape[1:])
+        want = source_shape(spec, source)
         if tuple(tensor.shape) != want:
             wrong.append((name, want, tuple(tensor.shape)))
             continue
@@ -116,7 +125,10 @@ def bind_tensors(targets, named_tensors, *, dtype, device, folder="<memory>",
         if key not in destinations:
             destinations[key] = torch.empty(
                 spec.shape, dtype=storage_dtype_of(spec, tensor.dtype, dtype), device=device)
-        destinations[key][source.row_start:source.row_start + source.rows].copy_(tensor)
+        rows = destinations[key][source.row_start:source.row_start + source.rows]
+        if source.cols is not None:
+            rows = rows[:, source.col_start:source.col_start + source.cols]
+        rows.copy_(tensor.reshape(rows.shape))
     missing = sorted(name for name in routes if name not in seen)
     if missing or unexpected or wrong:
         raise WeightsError(folder, missing, sorted(unexpected), wrong)

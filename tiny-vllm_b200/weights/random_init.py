@@ -18,6 +18,7 @@ from typing import Iterator
 
 import torch
 
+from .loader import source_shape
 
 NORMAL_STD = 0.02
 AROUND_ONE_SPREAD = 0.1
@@ -29,12 +30,14 @@ def random_tensors(targets, seed: int, device="cpu") -> Iterator[tuple[str, torc
     generator.manual_seed(seed)
     for _part, spec in targets:
         for source in spec.sources:
-            shape = (source.rows,) + tuple(spec.shape[1:])
+            shape = source_shape(spec, source)
             if spec.role == "integer":
                 raise ValueError(f"{source.name}: integer tables have no random law")
             if spec.init == "around_one":
                 t = torch.rand(shape, generator=generator, device=device, dtype=torch.float32)
                 t = 1.0 + (2.0 * t - 1.0) * AROUND_ONE_SPREAD
+            elif spec.init == "unit_interval":
+                t = torch.rand(shape, generator=generator, device=device, dtype=torch.float32)
             elif spec.init == "normal":
                 t = torch.randn(shape, generator=generator, device=device,
                                 dtype=torch.float32) * NORMAL_STD
