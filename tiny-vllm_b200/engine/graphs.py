@@ -195,7 +195,9 @@ class DecodeGraphs:
                 else:
                     tables[r, before[1]:len(table)] = table[before[1]:]
                     first_live = before[2]
-                # pages a window gave back read -1 from the first live entry backwards
+                # pages a window gave back read -1 from the first live entry backwards (behind the
+                # leading pages that a window with kept first tokens never gives back)
+                first_live = max(first_live, self.runner.manager.kept_pages(g))
                 while first_live < len(table) and table[first_live] < 0:
                     tables[r, first_live] = -1
                     first_live += 1

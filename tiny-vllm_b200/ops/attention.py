@@ -18,9 +18,14 @@ max(0, p - window + 1) to p through the block table.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import kernels
+
+# TINYVLLM_B200_WINDOW_TILES=0 keeps the windowed mixers on the row kernel (for comparison)
+TENSOR_CORE_WINDOWS = os.environ.get("TINYVLLM_B200_WINDOW_TILES", "1") != "0"
 
 # tokens up to which the row kernel spreads the chunks of a row over the grid
 SPLIT_MAX_TOKENS = 256
@@ -287,12 +292,46 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
         slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values,
         v_first=v_first, blend=mixer.vmix if v_first is not None else None)
     gate = projected[:, g_at:g_at + mixer.out_cols] if mixer.gate else None
+    queries = projected[:, q_at:q_at + mixer.q_cols]
+    heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, key_dim=mixer.key_dim,
+                 value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale)
+    if windowed_on_tensor_cores(mixer, projected, q_at, g_at, out):
+        # bfloat16: prompt portions in tiles of 64 tokens, single tokens (decoded ones, whose keys are in the
+        # cache by now) one CTA per kv head and chunk of keys
+        def singles(part):
+            need = kernels.attention_tiles_singles_floats(
+                part.stop - part.start, mixer.num_heads, mixer.value_dim, mixer.window, mixer.keep_first,
+                ctx.max_context)
+            kernels.attention_tiles_singles(
+                queries[part], keys, values, ctx.block_tables[group], ctx.positions[part], ctx.token_row[part],
+                **heads, max_context=ctx.max_context, scratch=ctx.workspace(need), out=out[part],
+                gate=None if gate is None else gate[part])
+
+        if ctx.decode_only:
+            singles(slice(0, ctx.num_tokens))
+            return
+        if ctx.tile_row is not None:
+            if ctx.tile_row.shape[0] > 0:
+                kernels.attention_tiles(queries, keys, values, ctx.block_tables[group], ctx.positions, ctx.tile_row,
+                                        ctx.tile_first, ctx.tile_count, **heads, out=out, gate=gate)
+            for first, count in ctx.single_runs:
+                singles(slice(first, first + count))
+            return
     scratch = None
     if ctx.split_chunks > 0:
         scratch = ctx.workspace(kernels.attention_rows_scratch_floats(
             ctx.num_tokens, mixer.num_heads, mixer.value_dim, ctx.split_chunks))
     kernels.attention_rows(
-        projected[:, q_at:q_at + mixer.q_cols], projected.stride(0), keys, values, ctx.block_tables[group],
+        queries, projected.stride(0), keys, values, ctx.block_tables[group],
         ctx.token_row, ctx.positions, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.key_dim,
         value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale,
         gate=gate, out=out, scratch=scratch, max_chunks=ctx.split_chunks)
+
+
+def windowed_on_tensor_cores(mixer, projected: torch.Tensor, q_at: int, g_at: int, out: torch.Tensor) -> bool:
+    """Whether the tensor-core kernels take this mixer's attention: bfloat16, key and value sizes
+    that are multiples of 16, 16-byte aligned query rows; everything else goes to the row kernel."""
+    return (projected.dtype == torch.bfloat16 and TENSOR_CORE_WINDOWS
+            and kernels.attention_tiles_supports(mixer.key_dim, mixer.value_dim, mixer.num_heads, mixer.num_kv_heads)
+            and projected.stride(0) % 8 == 0 and q_at % 8 == 0 and projected.data_ptr() % 16 == 0
+            and g_at % 2 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)

@@ -73,9 +73,26 @@ def _sources_of(name: str) -> list[Path]:
     return [found[key] for key in sorted(found)]
 
 
+def _split(name: str) -> tuple[str, tuple[str, ...]]:
+    """A library name is a source name, optionally followed by ``@MACRO=value,MACRO=value``: the
+    same source compiled with those macros set (one library per combination of sizes)."""
+    source, _, macros = name.partition("@")
+    return source, tuple(f"-D{item}" for item in macros.split(",") if item)
+
+
+def variant(source: str, **macros: int) -> str:
+    """Name of the library of ``source`` compiled with ``macros``."""
+    return source + "@" + ",".join(f"{key}={int(value)}" for key, value in sorted(macros.items()))
+
+
+def _file_stem(name: str) -> str:
+    return re.sub(r"[^A-Za-z0-9_]+", "-", name)
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS + EXTRA_LINK.get(name, ())).encode())
+    name, macros = _split(name)
+    h.update(" ".join(NVCC_FLAGS + macros + EXTRA_LINK.get(name, ())).encode())
     for path in _sources_of(name):
         h.update(path.name.encode())
         h.update(path.read_bytes())
@@ -102,7 +119,7 @@ def _usable_dir() -> Path:
 
 def library_path(name: str) -> Path | None:
     """Path of the up-to-date library of ``name`` if it has been built."""
-    filename = f"tvb200_{name}_{_digest(name)}.so"
+    filename = f"tvb200_{_file_stem(name)}_{_digest(name)}.so"
     for folder in _build_dirs():
         if (folder / filename).is_file():
             return folder / filename
@@ -111,20 +128,22 @@ def library_path(name: str) -> Path | None:
 
 def compile_library(name: str, *, verbose: bool = True) -> Path:
     """Compile ``csrc/<name>.cu`` unless its library is already there."""
-    source = CSRC / f"{name}.cu"
+    source_name, macros = _split(name)
+    source = CSRC / f"{source_name}.cu"
     if not source.is_file():
-        raise KernelBuildError(f"no CUDA source named {name!r} in {CSRC}")
+        raise KernelBuildError(f"no CUDA source named {source_name!r} in {CSRC}")
     existing = library_path(name)
     if existing is not None:
         return existing
     nvcc = _find_nvcc()
     folder = _usable_dir()
-    target = folder / f"tvb200_{name}_{_digest(name)}.so"
+    target = folder / f"tvb200_{_file_stem(name)}_{_digest(name)}.so"
     partial = folder / f".{target.name}.{os.getpid()}.{threading.get_ident()}.tmp"
-    command = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(partial), str(source),
-               *EXTRA_LINK.get(name, ())]
+    command = [nvcc, *NVCC_FLAGS, *macros, "-I", str(CSRC), "-o", str(partial), str(source),
+               *EXTRA_LINK.get(source_name, ())]
     if verbose:
-        print(f"[tinyvllm_b200] compiling {source.name} for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[tinyvllm_b200] compiling {source.name} {' '.join(macros)} for sm_100a ...".replace("  ", " "),
+              file=sys.stderr, flush=True)
     started = time.time()
     process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     while True:
@@ -139,7 +158,7 @@ def compile_library(name: str, *, verbose: bool = True) -> Path:
         partial.unlink(missing_ok=True)
         raise KernelBuildError(f"nvcc failed on {source.name}:\n{output}")
     os.replace(partial, target)
-    for stale in folder.glob(f"tvb200_{name}_*.so"):       # builds of older versions of this source
+    for stale in folder.glob(f"tvb200_{_file_stem(name)}_*.so"):       # builds of older versions of this source
         if stale != target:
             stale.unlink(missing_ok=True)
     if verbose:

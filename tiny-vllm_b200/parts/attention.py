@@ -199,7 +199,12 @@ class WindowedAttention(Part):
         return False
 
     def scratch_floats(self, rows: int, chunks: int) -> int:
-        return kernels.attention_rows_scratch_floats(rows, self.num_heads, self.value_dim, chunks)
+        """float32 scratch for ``rows`` single tokens whose keys span ``chunks`` chunks: what the row
+        kernel or the tensor-core kernel for single tokens asks for, whichever is more."""
+        span = chunks * kernels.attention_chunk_keys()
+        return max(kernels.attention_rows_scratch_floats(rows, self.num_heads, self.value_dim, chunks),
+                   kernels.attention_tiles_singles_floats(rows, self.num_heads, self.value_dim, self.window,
+                                                          self.keep_first, span))
 
     # ---------------------------------------------------------------- running
     def between(self, projected, at: int, ctx, out, run: int) -> None:
