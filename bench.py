@@ -685,6 +685,197 @@ def serving_workload(args) -> int:
     return 0
 
 
+# ------------------------------------------- Gumapel beside a windowed Qwen3 of equal layer sizes
+GUMAPEL_SIZES = {
+    # width, q heads, kv heads, head size, feed-forward width (the layers of the 0.6B, 8B and 32B sizes)
+    "0.6b": (1024, 16, 8, 128, 3072),
+    "8b": (4096, 32, 8, 128, 12288),
+    "32b": (5120, 64, 8, 128, 25600),
+}
+GUMAPEL_WINDOW, GUMAPEL_KEPT = 1024, 4
+# (kernel of the new design, its counterpart in the windowed Qwen3) by what they do
+LIKE_KERNELS = (
+    ("stream_norm", "rms_norm", "pre-norm + residual sum"),
+    ("qkv_prepare", "qk_norm_rope_store", "q/k norm or rotation + cache write"),
+    ("attention_tiles", "attention_prefill_tc", "prompt attention"),
+    ("attention_tiles_singles", "attention_decode", "decode attention"),
+    ("gated_act", "silu_mul", "act(gate) * up"),
+)
+
+
+class KernelClock:
+    """Times every call of the named functions of ``ops.kernels`` with CUDA events (the calls of one
+    eager step); ``totals()`` gives name -> (calls, milliseconds) after a synchronize."""
+
+    def __init__(self, names):
+        from tinyvllm_b200.ops import kernels
+        self.kernels, self.names, self.originals, self.marks = kernels, names, {}, []
+
+    def __enter__(self):
+        import torch
+        for name in self.names:
+            original = getattr(self.kernels, name)
+            self.originals[name] = original
+
+            def timed(*args, _original=original, _name=name, **kwargs):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                result = _original(*args, **kwargs)
+                end.record()
+                self.marks.append((_name, start, end))
+                return result
+            setattr(self.kernels, name, timed)
+        return self
+
+    def __exit__(self, *exc):
+        for name, original in self.originals.items():
+            setattr(self.kernels, name, original)
+
+    def totals(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for name, start, end in self.marks:
+            calls, ms = out.get(name, (0, 0.0))
+            out[name] = (calls + 1, ms + start.elapsed_time(end))
+        return out
+
+
+def gumapel_config(size: str, layers: int):
+    from tinyvllm_b200.models import GumapelConfig
+    from tinyvllm_b200.models.gumapel import GumapelLayer
+
+    width, heads, kv, dim, ff = GUMAPEL_SIZES[size]
+    made = []
+    for index in range(layers):
+        if index % 4 == 3:
+            made.append(GumapelLayer(type="attention", heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                     window=GUMAPEL_WINDOW, v_mix=True, ff=ff))
+        else:
+            made.append(GumapelLayer(type="attention_2", heads=heads, kv_heads=kv, dim=dim, vdim=dim,
+                                     scale=dim ** -0.5, window=GUMAPEL_WINDOW, keep_first=GUMAPEL_KEPT, rot_dims=dim,
+                                     rot_base=500000.0, v_mix=True, ff=ff))
+    return GumapelConfig(vocab=MODEL["vocab_size"], width=width, norm_eps=1e-6, layers=tuple(made))
+
+
+def windowed_qwen3_config(size: str, layers: int):
+    from tinyvllm_b200.models import Qwen3Config
+
+    width, heads, kv, dim, ff = GUMAPEL_SIZES[size]
+    return Qwen3Config(**{**MODELS["0.6b"], "hidden_size": width, "num_attention_heads": heads,
+                          "num_key_value_heads": kv, "head_dim": dim, "intermediate_size": ff,
+                          "num_hidden_layers": layers, "tie_word_embeddings": False,
+                          "layer_windows": (GUMAPEL_WINDOW,) * layers})
+
+
+def kernel_roofline(name: str, size: str, tokens: int, context: int, peak: dict) -> tuple[float, str]:
+    """Microseconds the kernel ``name`` needs at the measured peaks for one layer of ``size``: ``tokens``
+    new tokens whose requests hold ``context`` tokens each (a prompt: context == tokens)."""
+    width, heads, kv, dim, ff = GUMAPEL_SIZES[size]
+    seen = min(GUMAPEL_WINDOW, context)
+    bytes_, flops = 0.0, 0.0
+    if name == "stream_norm":
+        bytes_ = tokens * width * (4 + 4 + 4 + 2)
+    elif name == "rms_norm":
+        bytes_ = tokens * width * 2 * 4
+    elif name in ("qkv_prepare", "qk_norm_rope_store"):
+        bytes_ = tokens * dim * 2 * ((heads + 2 * kv) + heads + 2 * kv)
+    elif name in ("gated_act", "silu_mul"):
+        bytes_ = tokens * ff * 2 * 3
+    elif name in ("attention_tiles", "attention_prefill_tc", "attention_prefill"):
+        pairs = sum(min(p + 1, GUMAPEL_WINDOW) for p in range(tokens))       # (query, key) pairs seen
+        flops = 2.0 * heads * 2 * dim * pairs
+    elif name in ("attention_tiles_singles", "attention_decode"):
+        bytes_ = tokens * kv * seen * 2 * dim * 2
+    if flops:
+        return flops / (peak["bf16_tflops"] * 1e12) * 1e6, "tensor"
+    return bytes_ / (peak["hbm_gbs"] * 1e9) * 1e6, "memory"
+
+
+def gumapel_workload(args) -> int:
+    """Prefill and decode of Gumapel at the layer sizes of the 0.6B, 8B and 32B models (random
+    weights, ``--layers`` layers, default 4, window 1,024) beside a Qwen3 of the same sizes whose
+    layers all have that window: tokens/s through the engine, and every kernel of the new design
+    beside its counterpart with the fraction of its roofline.  One JSON line."""
+    import torch
+
+    from tinyvllm_b200 import EngineConfig
+    from tinyvllm_b200.engine.engine import Engine
+    from tinyvllm_b200.engine.step import StepEntry
+
+    layers = args.layers if args.layers_given else 4
+    batch, prompt, steps, warmup = args.batch, PROMPT_TOKENS, min(args.steps, 64), max(args.warmup, 3)
+    peak, peak_source = peaks()
+    names = sorted({n for pair in LIKE_KERNELS for n in pair[:2]} | {"attention_prefill", "attention_rows"})
+    results = []
+    sampler = ClockSampler()
+    sampler.start()
+    for size in GUMAPEL_SIZES:
+        row = {"size": size}
+        for label, config in (("gumapel", gumapel_config(size, layers)), ("qwen3_windowed", windowed_qwen3_config(size, layers))):
+            with tempfile.TemporaryDirectory() as folder:
+                Path(folder, "config.json").write_text(json.dumps(config.to_json()))
+                engine = Engine.from_config(EngineConfig(
+                    model=folder, dtype="bfloat16", weights="random", seed=0, max_model_len=CONTEXT_LIMIT,
+                    max_num_seqs=batch, max_num_batched_tokens=4096, prefill_chunk_size=2048,
+                    prefill_reserve_tokens=0, prefill_reserve_requests=0, kv_block_size=16,
+                    kv_cache_memory_bytes=2 * 1024**3, graph_batch_sizes=(batch,)))
+                decode = run_decode(engine, batch, steps, warmup, sampler, prompt_tokens=prompt)
+                prefill_ms = run_prefill(engine, repeats=5, tokens=prompt)
+                # one eager prompt step and one eager decode step, kernel by kernel
+                runner = engine.runner
+                rng = random.Random(5)
+                with torch.inference_mode():
+                    for r in range(batch):
+                        runner.open(f"k{r}")
+                    prompts = [StepEntry(f"k{r}", tuple(random_prompt(rng, prompt)), ()) for r in range(batch)]
+                    def eager_step(entries):
+                        plan = runner.plan(entries)
+                        runner.execute(runner.build_context(entries, plan))
+                        runner.manager.commit(plan)
+
+                    for entry in prompts[1:]:
+                        eager_step([entry])
+                    with KernelClock(names) as clock:
+                        eager_step([prompts[0]])
+                    by_prompt = clock.totals()
+                    singles = [StepEntry(f"k{r}", (1,), (0,)) for r in range(batch)]
+                    eager_step(singles)
+                    with KernelClock(names) as clock:
+                        eager_step(singles)
+                    by_decode = clock.totals()
+                    for r in range(batch):
+                        runner.close(f"k{r}")
+                kernels_out = {}
+                for phase, found, tokens in (("prefill", by_prompt, prompt), ("decode", by_decode, batch)):
+                    for name, (calls, ms) in sorted(found.items()):
+                        per_layer = 1e3 * ms / max(1, calls)
+                        ideal, bound = kernel_roofline(name, size, tokens, prompt, peak)
+                        kernels_out[f"{phase}:{name}"] = {
+                            "calls": calls, "us_per_call": round(per_layer, 2), "roofline_us": round(ideal, 2),
+                            "bound": bound, "frac": round(ideal / per_layer, 3) if per_layer > 0 else None}
+                row[label] = {
+                    "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                    "prefill_tokens_per_s": round(prompt / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                    "weight_bytes": engine.runner.model.weight_bytes(), "kernels": kernels_out}
+                engine.close()
+                del engine
+                torch.cuda.empty_cache()
+        results.append(row)
+    sampler.stop()
+    print(json.dumps({
+        "metric": "Gumapel beside a windowed Qwen3 of equal layer sizes: decode tok/s at batch "
+                  f"{batch} from context {prompt:,}, prefill tok/s of {prompt:,} tokens, bf16",
+        "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic (random weights and tokens)",
+        "config": {"layers": layers, "window": GUMAPEL_WINDOW, "kept_first": GUMAPEL_KEPT, "batch": batch,
+                   "vocab": MODEL["vocab_size"], "sizes": {k: list(v) for k, v in GUMAPEL_SIZES.items()},
+                   "timing": "CUDA events; decode replays graphs with inputs uploaded every step, caches of "
+                             f"{batch} requests larger than nothing is reused from; kernel figures are single eager calls"},
+        "peaks": {"hbm_gbs": peak["hbm_gbs"], "bf16_tflops": peak["bf16_tflops"], "source": peak_source},
+        "clocks": sampler.summary(), "results": results}))
+    return 0
+
+
 def arrivals_workload(args) -> int:
     """16 requests with prompts of 64 or 512 tokens and 64 new tokens that arrive 20 ms apart, at the
     0.6B sizes, through ``Engine.submit(arrival_ns=)`` and ``Engine.step``: time to first token, time
@@ -739,9 +930,10 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals"), default="0.6b",
+    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals", "gumapel"), default="0.6b",
                         help="0.6b: the decode and prefill measurement (default); 8b, 32b: the serving "
-                             "workloads of those sizes at full depth; arrivals: 16 requests 20 ms apart")
+                             "workloads of those sizes at full depth; arrivals: 16 requests 20 ms apart; "
+                             "gumapel: the Gumapel design beside a windowed Qwen3 at equal layer sizes")
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the configuration has (both numbers are in the line)")
     parser.add_argument("--batch", type=int, default=8)
@@ -764,6 +956,8 @@ def main() -> int:
         return serving_workload(args)
     if args.workload == "arrivals":
         return arrivals_workload(args)
+    if args.workload == "gumapel":
+        return gumapel_workload(args)
     if args.eager_profile:
         return eager_profile(args, warmup)
     return headline(args, warmup)
