@@ -82,14 +82,17 @@ def _caches(pages, kv, page, dk, dv, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("dk,dv", [(20, 24), (32, 24), (128, 64)])
 @pytest.mark.parametrize("norm,rot,pairing", [("unit", 0, "interleaved"), (None, 12, "interleaved"),
-                                              (None, 20, "interleaved"), ("weight", 8, "half_split")])
-def test_prepare_norm_rotation_blend_and_store(norm, rot, pairing, dtype):
-    """Heads of 20 keys and 24 values at positions up to 100,000, blended values, scattered slots."""
+                                              (None, 20, "interleaved"), ("weight", 8, "half_split"),
+                                              ("weight", 16, "interleaved")])
+def test_prepare_norm_rotation_blend_and_store(norm, rot, pairing, dk, dv, dtype):
+    """Heads of 20 keys and 24 values (the general kernel) and of 32 and 128 keys (in bfloat16: the
+    kernel of 16-byte words) at positions up to 100,000, blended values, scattered slots."""
     from tinyvllm_b200.ops import kernels
 
     g = torch.Generator().manual_seed(rot + 1)
-    tokens, heads, kv, dk, dv, page = 6, 4, 2, 20, 24, 4
+    tokens, heads, kv, page = 6, 4, 2, 4
     at = 8
     cols = at + heads * dk + kv * dk + kv * dv + 3
     proj = torch.randn(tokens, cols, generator=g).to(dtype)

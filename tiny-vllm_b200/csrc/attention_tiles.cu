@@ -16,12 +16,14 @@
 //   tiles    rows = up to 64 consecutive tokens of one prompt portion, one q head (grid: tiles
 //            x q heads); the result is divided, gated and stored.
 //   singles  rows = the q heads of one kv head for ONE token (decoded tokens; up to 64 heads a
-//            group); the token's keys are cut into chunks of 256 at absolute multiples of 256,
+//            group); the token's keys are cut into chunks of 128 at absolute multiples of 128,
 //            a CTA takes one chunk (grid: tokens x kv heads x chunks, chunks counted back from
 //            the token's own position, then the chunks of kept first keys) and leaves
 //            (max, sum, out) in scratch; a second kernel merges a row's chunks in ascending
 //            order, gates and stores.  The keys are read once per kv head, and what a row sums
-//            depends on its own position only, not on the batch it is in.
+//            depends on its own position only, not on the batch it is in.  With up to 16 heads a
+//            group the chunk comes in with one wave of copies and every warp takes 32 of its
+//            keys (attention_singles_kernel); larger groups walk the chunk tile by tile.
 #include "common.cuh"
 
 #ifndef TILES_KEY_DIM
@@ -35,7 +37,7 @@
 #define TL_BN 32
 #define TL_WARPS 4
 #define TL_PAD 8
-#define TL_CHUNK 256           // keys per CTA in the singles form
+#define TL_CHUNK 128           // keys per CTA in the singles form
 #define TL_LOG2E 1.4426950408889634f
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -74,8 +76,10 @@ struct TileArgs {
     float scale;
 };
 
+__device__ __forceinline__ int chunk_of_slot(int z, int window_chunks, int position, int lo, int kept);
+
 template <int KD, int VD, bool SINGLES>
-__global__ void __launch_bounds__(TL_WARPS * 32, 2) attention_tiles_kernel(const TileArgs a) {
+__global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const TileArgs a) {
     constexpr int KROW = KD + TL_PAD, VROW = VD + TL_PAD;
     constexpr int KCHUNKS = KD / 8, VCHUNKS = VD / 8;
     extern __shared__ __align__(16) unsigned char shared_raw[];
@@ -117,10 +121,8 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 2) attention_tiles_kernel(const
         if (SINGLES) {
             // chunk of this CTA: z < window_chunks counts back from the token's own chunk; the others are
             // the chunks of kept keys that lie wholly before the window's first chunk
-            const int z = blockIdx.z, own = first_position / TL_CHUNK, first_chunk = lo_first / TL_CHUNK;
-            int chunk;
-            if (z < a.window_chunks) { chunk = own - z; if (chunk < first_chunk) return; }
-            else { chunk = z - a.window_chunks; if (chunk >= first_chunk || chunk * TL_CHUNK >= kept) return; }
+            const int chunk = chunk_of_slot(blockIdx.z, a.window_chunks, first_position, lo_first, kept);
+            if (chunk < 0) return;
             const int t0 = chunk * (TL_CHUNK / TL_BN), t1 = t0 + TL_CHUNK / TL_BN - 1;
             na = max(0, min(kept_tiles - 1, t1) - t0 + 1);
             a0 = t0;
@@ -180,14 +182,9 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 2) attention_tiles_kernel(const
     cp_async_wait<1>();                                   // the Q rows (the first group) have landed
     __syncthreads();
     const bool busy = warp * 16 < count;                  // a warp without rows only helps to load
-    uint32_t q_frag[KD / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < KD / 16; ++ks) {
-        const int matrix = lane >> 3;
-        const int r = warp * 16 + (lane & 7) + (matrix & 1) * 8;
-        const int c = ks * 16 + (matrix >> 1) * 8;
-        ldmatrix_x4(q_frag[ks], q_s + r * KROW + c);
-    }
+    // this lane's address in the Q rows for ldmatrix: the fragments are read again for every key tile
+    // (shared memory has the bandwidth; the registers they would hold let a third CTA onto the SM)
+    const bf16* q_lane = q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + (lane >> 4) * 8;
 
     const int g = lane >> 2, t4 = lane & 3;
     const int row_a = warp * 16 + g, row_b = row_a + 8;
@@ -226,6 +223,8 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 2) attention_tiles_kernel(const
             for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < KD / 16; ++ks) {
+            uint32_t q_frag[4];
+            ldmatrix_x4(q_frag, q_lane + ks * 16);
 #pragma unroll
             for (int np = 0; np < TL_BN / 16; ++np) {
                 uint32_t b[4];
@@ -233,8 +232,8 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 2) attention_tiles_kernel(const
                 const int key = np * 16 + (matrix >> 1) * 8 + (lane & 7);
                 const int dim = ks * 16 + (matrix & 1) * 8;
                 ldmatrix_x4(b, k_tile + key * KROW + dim);
-                mma_bf16(s_acc[2 * np], q_frag[ks], b[0], b[1]);
-                mma_bf16(s_acc[2 * np + 1], q_frag[ks], b[2], b[3]);
+                mma_bf16(s_acc[2 * np], q_frag, b[0], b[1]);
+                mma_bf16(s_acc[2 * np + 1], q_frag, b[2], b[3]);
             }
         }
 
@@ -288,16 +287,27 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 2) attention_tiles_kernel(const
 #pragma unroll
         for (int kk = 0; kk < TL_BN / 16; ++kk) {
 #pragma unroll
-            for (int dp = 0; dp < VD / 16; ++dp) {
-                uint32_t b[4];
+            for (int dp = 0; dp < VD / 16; dp += 2) {
+                // two blocks of 16 dimensions at a time, so that the product with the rest of a weight
+                // follows the product with its head on the same accumulator four instructions later, not two
+                uint32_t b[4], c[4];
                 const int matrix = lane >> 3;
                 const int key = kk * 16 + (matrix & 1) * 8 + (lane & 7);
                 const int dim = dp * 16 + (matrix >> 1) * 8;
                 ldmatrix_x4_trans(b, v_tile + key * VROW + dim);
+                if (dp + 1 < VD / 16) ldmatrix_x4_trans(c, v_tile + key * VROW + dim + 16);
                 mma_bf16(o_acc[2 * dp], p_hi[kk], b[0], b[1]);
                 mma_bf16(o_acc[2 * dp + 1], p_hi[kk], b[2], b[3]);
+                if (dp + 1 < VD / 16) {
+                    mma_bf16(o_acc[2 * dp + 2], p_hi[kk], c[0], c[1]);
+                    mma_bf16(o_acc[2 * dp + 3], p_hi[kk], c[2], c[3]);
+                }
                 mma_bf16(o_acc[2 * dp], p_lo[kk], b[0], b[1]);
                 mma_bf16(o_acc[2 * dp + 1], p_lo[kk], b[2], b[3]);
+                if (dp + 1 < VD / 16) {
+                    mma_bf16(o_acc[2 * dp + 2], p_lo[kk], c[0], c[1]);
+                    mma_bf16(o_acc[2 * dp + 3], p_lo[kk], c[2], c[3]);
+                }
             }
         }
     }
@@ -348,8 +358,205 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 2) attention_tiles_kernel(const
     }
 }
 
-// One warp per (token, head): the chunks of the row in ascending order of their keys (kept first
-// keys, then the window from its oldest chunk to the token's own), divided, gated, stored.
+// Which chunk the CTA with index z of a token takes: z < window_chunks counts back from the token's own
+// chunk; the others are the chunks of kept keys that lie wholly before the window's first chunk.
+// Returns -1 where there is nothing to do.
+__device__ __forceinline__ int chunk_of_slot(int z, int window_chunks, int position, int lo, int kept) {
+    const int own = position / TL_CHUNK, first_chunk = lo / TL_CHUNK;
+    if (z < window_chunks) {
+        const int chunk = own - z;
+        return chunk < first_chunk ? -1 : chunk;
+    }
+    const int chunk = z - window_chunks;
+    return (chunk >= first_chunk || chunk * TL_CHUNK >= kept) ? -1 : chunk;
+}
+
+// Single tokens, up to 16 q heads a kv head: one chunk of TL_CHUNK keys a CTA, all of it copied in at
+// once; warp w takes the keys w * 32 .. w * 32 + 31 of the chunk, the four partial results are merged in
+// shared memory in the order of the keys and leave as one (max, sum, out) per head.
+template <int KD, int VD>
+__global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_singles_kernel(const TileArgs a) {
+    constexpr int KROW = KD + TL_PAD, VROW = VD + TL_PAD;
+    constexpr int KCHUNKS = KD / 8, VCHUNKS = VD / 8;
+    static_assert(TL_CHUNK == TL_WARPS * TL_BN, "a warp takes one tile of the chunk");
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(shared_raw);                         // [16][KROW]
+    bf16* k_s = q_s + 16 * KROW;                                             // [chunk][KROW]
+    bf16* v_s = k_s + TL_CHUNK * KROW;                                       // [chunk][VROW]
+    int* slot_s = reinterpret_cast<int*>(v_s + TL_CHUNK * VROW);             // [chunk]
+    float* part_s = reinterpret_cast<float*>(k_s);                           // over K and V once they are used up
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int token = blockIdx.x;
+    const int request = a.token_row[token], position = a.positions[token];
+    if (request < 0 || position < 0) return;                 // a padding row; the merge writes its zeros
+    const int group = a.num_q / a.num_kv, kv_head = blockIdx.y, head0 = kv_head * group;
+    const int lo = a.window > 0 ? max(0, position - a.window + 1) : 0;
+    const int kept = min(a.keep_first, lo);
+    const int chunk = chunk_of_slot(blockIdx.z, a.window_chunks, position, lo, kept);
+    if (chunk < 0) return;
+    const int key0 = chunk * TL_CHUNK;
+    const int* table = a.block_tables + (int64_t)request * a.table_stride;
+
+    {   // where each key of the chunk lies; keys the token does not see are not even fetched
+        const int key = key0 + tid;
+        int slot = -1;
+        if (key <= position && (key >= lo || key < kept)) {
+            const int page = table[key / a.page_size];
+            if (page >= 0) slot = (page * a.num_kv + kv_head) * a.page_size + key % a.page_size;
+        }
+        slot_s[tid] = slot;
+    }
+    for (int index = tid; index < 16 * KCHUNKS; index += TL_WARPS * 32) {
+        const int r = index / KCHUNKS, c = index % KCHUNKS;
+        cp_async_16(q_s + r * KROW + c * 8,
+                    a.q + (int64_t)token * a.q_token_stride + (int64_t)(head0 + min(r, group - 1)) * KD + c * 8, r < group);
+    }
+    __syncthreads();
+    for (int index = tid; index < TL_CHUNK * KCHUNKS; index += TL_WARPS * 32) {
+        const int r = index / KCHUNKS, c = index % KCHUNKS;
+        const int slot = slot_s[r];
+        cp_async_16(k_s + r * KROW + c * 8, a.key_cache + (int64_t)max(slot, 0) * KD + c * 8, slot >= 0);
+    }
+    for (int index = tid; index < TL_CHUNK * VCHUNKS; index += TL_WARPS * 32) {
+        const int r = index / VCHUNKS, c = index % VCHUNKS;
+        const int slot = slot_s[r];
+        cp_async_16(v_s + r * VROW + c * 8, a.value_cache + (int64_t)max(slot, 0) * VD + c * 8, slot >= 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const int g = lane >> 2, t4 = lane & 3;
+    const int tile_key = key0 + warp * TL_BN;
+    const bool any = tile_key <= position && (tile_key + TL_BN - 1 >= lo || tile_key < kept);
+    float o_acc[VD / 8][4];
+#pragma unroll
+    for (int n = 0; n < VD / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.0f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+    if (any) {
+        const bf16* k_tile = k_s + warp * TL_BN * KROW;
+        const bf16* v_tile = v_s + warp * TL_BN * VROW;
+        const bf16* q_lane = q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * KROW + (lane >> 4) * 8;
+        float s_acc[TL_BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < TL_BN / 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < KD / 16; ++ks) {
+            uint32_t q_frag[4];
+            ldmatrix_x4(q_frag, q_lane + ks * 16);
+#pragma unroll
+            for (int np = 0; np < TL_BN / 16; ++np) {
+                uint32_t b[4];
+                const int matrix = lane >> 3;
+                const int key = np * 16 + (matrix >> 1) * 8 + (lane & 7);
+                const int dim = ks * 16 + (matrix & 1) * 8;
+                ldmatrix_x4(b, k_tile + key * KROW + dim);
+                mma_bf16(s_acc[2 * np], q_frag, b[0], b[1]);
+                mma_bf16(s_acc[2 * np + 1], q_frag, b[2], b[3]);
+            }
+        }
+        const float scale_log2 = a.scale * TL_LOG2E;
+#pragma unroll
+        for (int n = 0; n < TL_BN / 8; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = tile_key + n * 8 + 2 * t4 + (i & 1);
+                float s = s_acc[n][i] * scale_log2;
+                if (!(key <= position && (key >= lo || key < kept))) s = -INFINITY;
+                s_acc[n][i] = s;
+                if (i < 2) m_a = fmaxf(m_a, s); else m_b = fmaxf(m_b, s);
+            }
+        }
+        m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 1));
+        m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 2));
+        m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 1));
+        m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 2));
+        uint32_t p_hi[TL_BN / 16][4], p_lo[TL_BN / 16][4];
+#pragma unroll
+        for (int n = 0; n < TL_BN / 8; ++n) {
+            const float p0 = exp2f(s_acc[n][0] - m_a), p1 = exp2f(s_acc[n][1] - m_a);      // the tile has a key every row sees
+            const float p2 = exp2f(s_acc[n][2] - m_b), p3 = exp2f(s_acc[n][3] - m_b);
+            l_a += p0 + p1;
+            l_b += p2 + p3;
+            split_pair(p0, p1, p_hi[n >> 1][(n & 1) * 2], p_lo[n >> 1][(n & 1) * 2]);
+            split_pair(p2, p3, p_hi[n >> 1][(n & 1) * 2 + 1], p_lo[n >> 1][(n & 1) * 2 + 1]);
+        }
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+#pragma unroll
+        for (int kk = 0; kk < TL_BN / 16; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < VD / 16; dp += 2) {
+                // two blocks of 16 dimensions at a time, so that the product with the rest of a weight
+                // follows the product with its head on the same accumulator four instructions later, not two
+                uint32_t b[4], c[4];
+                const int matrix = lane >> 3;
+                const int key = kk * 16 + (matrix & 1) * 8 + (lane & 7);
+                const int dim = dp * 16 + (matrix >> 1) * 8;
+                ldmatrix_x4_trans(b, v_tile + key * VROW + dim);
+                if (dp + 1 < VD / 16) ldmatrix_x4_trans(c, v_tile + key * VROW + dim + 16);
+                mma_bf16(o_acc[2 * dp], p_hi[kk], b[0], b[1]);
+                mma_bf16(o_acc[2 * dp + 1], p_hi[kk], b[2], b[3]);
+                if (dp + 1 < VD / 16) {
+                    mma_bf16(o_acc[2 * dp + 2], p_hi[kk], c[0], c[1]);
+                    mma_bf16(o_acc[2 * dp + 3], p_hi[kk], c[2], c[3]);
+                }
+                mma_bf16(o_acc[2 * dp], p_lo[kk], b[0], b[1]);
+                mma_bf16(o_acc[2 * dp + 1], p_lo[kk], b[2], b[3]);
+                if (dp + 1 < VD / 16) {
+                    mma_bf16(o_acc[2 * dp + 2], p_lo[kk], c[0], c[1]);
+                    mma_bf16(o_acc[2 * dp + 3], p_lo[kk], c[2], c[3]);
+                }
+            }
+        }
+    }
+    __syncthreads();                                      // every warp is done with K and V: the partials go there
+    float* pm = part_s;                                   // [warps][16]
+    float* pl = pm + TL_WARPS * 16;                       // [warps][16]
+    float* po = pl + TL_WARPS * 16;                       // [warps][16][VD]
+    if (t4 == 0) {
+        pm[warp * 16 + g] = m_a; pm[warp * 16 + g + 8] = m_b;
+        pl[warp * 16 + g] = l_a; pl[warp * 16 + g + 8] = l_b;
+    }
+#pragma unroll
+    for (int n = 0; n < VD / 8; ++n) {
+        const int dim = n * 8 + 2 * t4;
+        float* ra = po + ((warp * 16 + g) * VD + dim);
+        float* rb = po + ((warp * 16 + g + 8) * VD + dim);
+        ra[0] = o_acc[n][0]; ra[1] = o_acc[n][1];
+        rb[0] = o_acc[n][2]; rb[1] = o_acc[n][3];
+    }
+    __syncthreads();
+    const int slots = a.window_chunks + a.kept_chunks;
+    for (int index = tid; index < group * VD; index += TL_WARPS * 32) {
+        const int row = index / VD, dim = index % VD;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < TL_WARPS; ++w) top = fmaxf(top, pm[w * 16 + row]);
+        float sum = 0.0f, out = 0.0f;
+#pragma unroll
+        for (int w = 0; w < TL_WARPS; ++w) {
+            const float m = pm[w * 16 + row];
+            const float weight = m == -INFINITY ? 0.0f : exp2f(m - top);
+            sum += pl[w * 16 + row] * weight;
+            out += po[(w * 16 + row) * VD + dim] * weight;
+        }
+        float* dst = a.scratch + (((int64_t)token * a.num_q + head0 + row) * slots + blockIdx.z) * (VD + 2);
+        if (dim == 0) { dst[0] = top; dst[1] = sum; }
+        dst[2 + dim] = out;
+    }
+}
+
+// One warp per (token, head): the partial results of the row's chunks, in ascending order of their keys
+// (kept first keys, then the window from its oldest chunk to the token's own), divided, gated, stored.
+// The largest maximum is found first, so that the sums do not wait for one another.
 template <int VD>
 __global__ void merge_singles_kernel(const TileArgs a, int tokens) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -367,28 +574,30 @@ __global__ void merge_singles_kernel(const TileArgs a, int tokens) {
     const int own = position / TL_CHUNK, first_chunk = lo / TL_CHUNK;
     const int slots = a.window_chunks + a.kept_chunks;
     const float* base = a.scratch + row * slots * (int64_t)(VD + 2);
+    // the row's slots in ascending key order: n_kept chunks of kept keys, then own - first_chunk + 1 of the window
+    const int n_kept = min(min(first_chunk, a.kept_chunks), (kept + TL_CHUNK - 1) / TL_CHUNK);
+    const int n_window = own - first_chunk + 1;
+    auto slot_of = [&](int i) { return i < n_kept ? a.window_chunks + i : n_window - 1 - (i - n_kept); };
+    const int count = n_kept + n_window;
+    float top = -INFINITY;
+    for (int i = lane; i < count; i += 32) top = fmaxf(top, base[(int64_t)slot_of(i) * (VD + 2)]);
+    top = warp_max(top);
     constexpr int PER = (VD + 31) / 32;
-    float m = -INFINITY, l = 0.0f, o[PER];
+    float l = 0.0f, o[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) o[i] = 0.0f;
-    auto take = [&](int z) {
-        const float* src = base + (int64_t)z * (VD + 2);
-        const float pm = src[0], pl = src[1];
-        if (pm == -INFINITY) return;
-        const float nm = fmaxf(m, pm);
-        const float s_old = m == -INFINITY ? 0.0f : exp2f(m - nm), s_new = exp2f(pm - nm);
-        l = l * s_old + pl * s_new;
+#pragma unroll 4
+    for (int i = 0; i < count; ++i) {
+        const float* src = base + (int64_t)slot_of(i) * (VD + 2);
+        const float m = src[0];
+        const float weight = m == -INFINITY ? 0.0f : exp2f(m - top);
+        l += src[1] * weight;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int dim = lane + 32 * i;
-            if (dim < VD) o[i] = o[i] * s_old + src[2 + dim] * s_new;
+        for (int j = 0; j < PER; ++j) {
+            const int dim = lane + 32 * j;
+            if (dim < VD) o[j] += src[2 + dim] * weight;
         }
-        m = nm;
-    };
-    for (int chunk = 0; chunk < first_chunk && chunk * TL_CHUNK < kept && chunk < a.kept_chunks; ++chunk)
-        take(a.window_chunks + chunk);
-    for (int chunk = first_chunk; chunk <= own; ++chunk)
-        if (own - chunk < a.window_chunks) take(own - chunk);
+    }
     const float inv = 1.0f / l;
     const bf16* gate = a.gate ? a.gate + (int64_t)token * a.gate_token_stride + (int64_t)head * VD : nullptr;
 #pragma unroll
@@ -478,12 +687,22 @@ extern "C" int tvb_attention_tiles_singles(const void* q, long long q_token_stri
         return TVB_BAD_ARGUMENT;
     singles_chunks(a.window, a.keep_first, max_context, &a.window_chunks, &a.kept_chunks);
     if (a.window_chunks + a.kept_chunks > 65535) return TVB_BAD_ARGUMENT;
-    auto kernel = attention_tiles_kernel<TILES_KEY_DIM, TILES_VALUE_DIM, true>;
-    const size_t shared = tiles_shared_bytes();
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    if (e != cudaSuccess) return (int)e;
     cudaStream_t s = (cudaStream_t)stream;
-    kernel<<<dim3(tokens, num_kv, a.window_chunks + a.kept_chunks), TL_WARPS * 32, shared, s>>>(a);
+    const dim3 grid(tokens, num_kv, a.window_chunks + a.kept_chunks);
+    if (num_q / num_kv <= 16) {
+        auto kernel = attention_singles_kernel<TILES_KEY_DIM, TILES_VALUE_DIM>;
+        const size_t shared = (size_t)(16 + TL_CHUNK) * (TILES_KEY_DIM + TL_PAD) * sizeof(bf16) +
+                              (size_t)TL_CHUNK * (TILES_VALUE_DIM + TL_PAD) * sizeof(bf16) + TL_CHUNK * sizeof(int);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<grid, TL_WARPS * 32, shared, s>>>(a);
+    } else {
+        auto kernel = attention_tiles_kernel<TILES_KEY_DIM, TILES_VALUE_DIM, true>;
+        const size_t shared = tiles_shared_bytes();
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<grid, TL_WARPS * 32, shared, s>>>(a);
+    }
     const int64_t rows = (int64_t)tokens * num_q;
     merge_singles_kernel<TILES_VALUE_DIM><<<(unsigned)((rows + TL_WARPS - 1) / TL_WARPS), TL_WARPS * 32, 0, s>>>(a, tokens);
     return tvb_last_error();

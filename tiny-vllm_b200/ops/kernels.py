@@ -391,7 +391,8 @@ def stream_norm(stream: torch.Tensor | None, weight: torch.Tensor | None, eps: f
     _check(fn(_ptr(stream), _ptr(add), _ptr(add2), dtype_tag(add.dtype) if add is not None else F32,
               _ptr(weight) if want_output else None,
               dtype_tag(weight.dtype) if weight is not None else dtype_tag(out_dtype), _ptr(y),
-              dtype_tag(out_dtype), _ptr(stream_out), _ptr(rows), count, width, eps, 0, _stream()), "stream_norm")
+              dtype_tag(out_dtype), _ptr(stream_out), _ptr(rows), count, width, eps, _pdl("norm"), _stream()),
+           "stream_norm")
     return y, stream_out
 
 
@@ -499,7 +500,7 @@ def qkv_prepare(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, num_q: i
 
 
 # ----------------- windowed attention on the tensor cores, compiled per (key size, value size)
-TILES_CHUNK_KEYS = 256
+TILES_CHUNK_KEYS = 128
 
 
 def _tiles_library(key_dim: int, value_dim: int) -> str:
@@ -579,7 +580,7 @@ def attention_tiles_singles(q: torch.Tensor, key_cache: torch.Tensor, value_cach
                             keep_first: int, scale: float, max_context: int, scratch: torch.Tensor,
                             out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
     """The same attention for single tokens whose keys and values are in the cache already (decoded
-    tokens): a CTA serves the q heads of one kv head over one chunk of 256 keys, a second launch
+    tokens): a CTA serves the q heads of one kv head over one chunk of 128 keys, a second launch
     merges a row's chunks.  Token i is of request row ``token_row[i]`` (-1: padding, zeros come out)
     at ``positions[i]`` < ``max_context``; ``scratch``: float32, :func:`attention_tiles_singles_floats`."""
     _need_cuda(q, key_cache, value_cache, block_tables, positions, token_row, out, gate, scratch)
