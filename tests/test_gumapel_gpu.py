@@ -255,7 +255,7 @@ def test_attention_sees_exactly_its_window_and_the_kept_first_keys(kind, dtype, 
 
 @pytest.mark.parametrize("kind,dtype", ATTENTION_KINDS, ids=[f"{k}-{'f32' if d == torch.float32 else 'bf16'}"
                                                              for k, d in ATTENTION_KINDS])
-@pytest.mark.parametrize("group,dk,dv", [(1, 16, 64), (3, 48, 32), (8, 64, 16)])
+@pytest.mark.parametrize("group,dk,dv", [(1, 16, 64), (3, 48, 32), (8, 64, 16), (20, 16, 32)])
 def test_attention_values_with_a_gate(kind, dtype, group, dk, dv):
     """Random queries of several requests in one launch against the plain attention, gated."""
     kv, page, window, keep, scale = 2, 8, 45, 6, 0.2
