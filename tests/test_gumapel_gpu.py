@@ -449,3 +449,26 @@ def test_bfloat16_generation_runs_on_the_tensor_core_kernels(folders, monkeypatc
         if (top[0] - top[1]).item() > 0.05 * logits.abs().max().item():
             assert output.output_token_ids[0] == int(logits.argmax())
     assert math.isfinite(sum(sum(o.output_token_ids) for o in outputs))
+
+
+def test_command_line(folders, capsys):
+    """python -m tinyvllm_b200 on a Gumapel folder: greedy tokens of the plain implementation, also
+    streamed, and with weights drawn from a seed instead of the file."""
+    from tinyvllm_b200.__main__ import main
+
+    name = "r"
+    prompts = [tokens_of(GUMAPEL_CONFIGS[name].vocab, n, 950 + n) for n in (3, 45)]
+    want = [greedy_oracle(folders[name], prompt, 10) for prompt in prompts]
+    common = ["--model", str(folders[name]), "--max-new-tokens", "10", "--ignore-eos", "--kv-cache-mib", "16",
+              "--max-model-len", "256", "--kv-block-size", "16"]
+    ids = [arg for prompt in prompts for arg in ("--prompt-ids", ",".join(map(str, prompt)))]
+    main(common + ["--dtype", "float32", "--stream"] + ids)
+    lines = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    streamed = {0: [], 1: []}
+    for line in lines[:-1]:
+        streamed[line["prompt"]].append(line["token_id"])
+    assert [streamed[0], streamed[1]] == want
+    assert [record["output_token_ids"] for record in lines[-1]["outputs"]] == want
+    main(common + ["--dtype", "bfloat16", "--random-weights", "7"] + ids)
+    records = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["outputs"]
+    assert [len(record["output_token_ids"]) for record in records] == [10, 10]
