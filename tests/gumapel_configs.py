@@ -2,7 +2,7 @@
 
 The configurations differ in everything config.json can say: width, vocabulary, number and order
 of layers, heads and groups (1, 2, 3 and 4 query heads a kv head), key and value sizes (equal or
-not, multiples of 16 or not), rotated dimensions (all or part of a head), windows (shorter than a
+not, multiples of 16 or not, one odd), rotated dimensions (all or part of a head), windows (shorter than a
 page, longer than a chunk of 256 keys, none), kept first tokens (none, fewer than a page, more
 than a page), layers without a feed-forward, layers that take no part in value blending, and a
 first blending layer that is not the first layer.  Weights are drawn with a spread of
@@ -44,7 +44,7 @@ GUMAPEL_CONFIGS = {
     "q": GumapelConfig(vocab=97, width=48, norm_eps=1e-6, layers=(
         _a(3, 1, 24, 40, 9, v_mix=False, ff=64),
         _b(6, 2, 24, 40, 33, 5, 12, 1000000.0, ff=80),
-        _a(6, 2, 8, 40, None, ff=None),
+        _a(6, 2, 9, 40, None, ff=None),
         _b(6, 2, 24, 40, 33, 5, 12, 1000000.0, ff=80))),
     # one head a group, equal key and value size 64, a window of one page exactly, nothing kept
     "r": GumapelConfig(vocab=130, width=128, norm_eps=1e-6, layers=(

@@ -82,7 +82,7 @@ def _caches(pages, kv, page, dk, dv, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("dk,dv", [(20, 24), (32, 24), (128, 64)])
+@pytest.mark.parametrize("dk,dv", [(20, 24), (21, 7), (32, 24), (128, 64)])
 @pytest.mark.parametrize("norm,rot,pairing", [("unit", 0, "interleaved"), (None, 12, "interleaved"),
                                               (None, 20, "interleaved"), ("weight", 8, "half_split"),
                                               ("weight", 16, "interleaved")])

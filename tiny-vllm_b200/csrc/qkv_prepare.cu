@@ -136,9 +136,15 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_kernel(
                 squares = __fadd_rn(squares, __fmaf_rn(a[i], a[i], __fmul_rn(b[i], b[i])));
             }
         }
+        // a head of an odd size has one value without a partner (never turned): lane 0 carries it
+        const bool lone_here = (key_dim & 1) && lane == 0;
+        float lone = lone_here ? to_float<T>(src[key_dim - 1]) : 0.0f;
+        squares = __fmaf_rn(lone, lone, squares);
         if (norm_mode != PREP_NORM_NONE) {
             squares = warp_sum(squares);
             const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, (float)key_dim), eps)));
+            lone = __fmul_rn(lone, inverse_rms);
+            if (weight && lone_here) lone = __fmul_rn(lone, to_float<W>(weight[key_dim - 1]));
 #pragma unroll
             for (int i = 0; i < PAIRS; ++i) {
                 if (lane + 32 * i < pairs) {
@@ -165,6 +171,7 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_kernel(
                 else { dst[at_a[i]] = from_float<T>(u); dst[at_b[i]] = from_float<T>(v); }
             }
         }
+        if (lone_here) dst[key_dim - 1] = from_float<T>(lone);
     }
 }
 
@@ -277,7 +284,7 @@ extern "C" int tvb_qkv_prepare(void* proj, long long token_stride, int q_at, int
                                void* key_cache, void* value_cache, int page_size, const void* v_first,
                                long long v_first_stride, const void* blend, int tokens, int dtype, void* stream) {
     if (tokens <= 0) return 0;
-    if (key_dim <= 0 || key_dim % 2 || key_dim > 64 * PREP_MAX_PAIRS || value_dim <= 0 || num_q <= 0 || num_kv < 0 ||
+    if (key_dim <= 0 || key_dim > 64 * PREP_MAX_PAIRS || value_dim <= 0 || num_q <= 0 || num_kv < 0 ||
         num_q + 2 * num_kv > 65535 * PREP_WARPS || (slots && page_size <= 0) || norm_mode < 0 || norm_mode > 2 ||
         (norm_mode == PREP_NORM_WEIGHT && (!q_weight || !k_weight)) ||
         (inv_freq && (rot_dims <= 0 || rot_dims % 2 || rot_dims > key_dim || pairing < 0 || pairing > 1)) ||

@@ -68,8 +68,6 @@ class GumapelLayer:
             _positive_int(f"mixer.{name}", getattr(self, name))
         if self.heads % self.kv_heads:
             raise ConfigError("mixer.heads must be a multiple of mixer.kv_heads")
-        if self.dim % 2:
-            raise ConfigError("mixer.dim must be even")
         if self.window is not None:
             _positive_int("mixer.mask.size", self.window)
         if type(self.keep_first) is not int or self.keep_first < 0:

@@ -458,8 +458,8 @@ def qkv_prepare(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, num_q: i
     if min(q_at, k_at, v_at) < 0 or max(q_at + num_q * key_dim, k_at + num_kv * key_dim,
                                         v_at + num_kv * value_dim) > proj.shape[1]:
         raise KernelError("qkv_prepare: the heads do not fit the projection's rows")
-    if key_dim % 2 or key_dim > 256 or value_dim > 256:
-        raise KernelError(f"qkv_prepare takes even key sizes and sizes up to 256, not {key_dim} / {value_dim}")
+    if key_dim > 256 or value_dim > 256:
+        raise KernelError(f"qkv_prepare takes key and value sizes up to 256, not {key_dim} / {value_dim}")
     if positions.dtype != torch.int32 or positions.shape != (tokens,):
         raise KernelError("qkv_prepare: positions must be int32 [tokens]")
     if norm not in NORM_MODES or pairing not in PAIRINGS:

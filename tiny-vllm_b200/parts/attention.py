@@ -116,9 +116,8 @@ class WindowedAttention(Part):
                  value_mix_key: str = "v_first", names: dict | None = None, hosted: bool = False) -> None:
         if num_heads % num_kv_heads:
             raise ValueError("query heads must be a multiple of key-value heads")
-        if key_dim % 2 or not 0 < key_dim <= 256 or not 0 < value_dim <= 256:
-            raise ValueError(f"the attention kernels take even key sizes and sizes up to 256, "
-                             f"not {key_dim} / {value_dim}")
+        if not 0 < key_dim <= 256 or not 0 < value_dim <= 256:
+            raise ValueError(f"the attention kernels take key and value sizes up to 256, not {key_dim} / {value_dim}")
         if qk_norm not in (None, "unit", "weight"):
             raise ValueError(f"qk_norm is None, 'unit' or 'weight', not {qk_norm!r}")
         if value_mix not in (None, "first", "blend"):
