@@ -5,8 +5,9 @@ the package's weight-streaming kernel for small weights (measured against cuBLAS
 wins up to 8 rows by 20 to 50 %, is level around 16 and loses beyond, and loses on large
 weights).  Up to 64 rows and a weight of 400 MB and more (the gate/up product of the largest
 models): the package's stream-k tcgen05 kernel, which reads the weight faster than cuBLAS but has
-a higher fixed cost per launch (figures at STREAM_MIN_WEIGHT_BYTES).  Results in float32 (the
-logits: vocabulary x width) go to cuBLAS with float32 output at every row count: 53 us against
+a higher fixed cost per launch (figures at STREAM_MIN_WEIGHT_BYTES).  Results in float32 of weights
+beyond the small-weight kernel's limit (the logits: vocabulary x width) go to cuBLAS with float32
+output at every row count: 53 us against
 84 us (small-weight kernel) and 56 us (stream-k kernel) at 8 rows.  The packed gate/up product
 with its activation at 128 rows and more (prefill): the package's tcgen05 kernel, which keeps
 the accumulator in tensor memory and applies SiLU(gate) * up on the way out.  The other
@@ -96,6 +97,10 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype
         # float32 results (logits) keep the float32 accumulator unrounded
         if streamed(x, weight, kernels.GEMM_F32) and (out is None or out.stride(1) == 1):
             return kernels.gemm_stream(x, weight, kernels.GEMM_F32, out=out)
+        if small(x, weight) and (out is None or out.stride(1) == 1):
+            # few rows and a small weight (an output projection that leaves a float32 sum; the head of a
+            # small vocabulary): the weight-streaming kernel, as for the bfloat16 results
+            return kernels.gemm_small_m(x, weight, kernels.GEMM_F32, out=out, prefetch=next_weight(weight))
         if x.stride(1) == 1 and weight.stride(1) == 1 and x.shape[1] % 8 == 0:
             result = torch.mm(x, weight.t(), out_dtype=torch.float32)
         elif x.shape[0] <= 256:
