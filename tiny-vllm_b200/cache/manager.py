@@ -39,6 +39,7 @@ class CacheGroup:
     window: int | None = None
     value_dim: int | None = None          # size of a value, if not head_dim
     keep_first: int = 0                   # first tokens a window never lets go of
+    value_offset: int | None = None       # values are a part of the key rows, from this element on
 
     @property
     def value_size(self) -> int:

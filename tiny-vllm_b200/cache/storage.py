@@ -1,6 +1,6 @@
 """Device side of the cache: page tensors of every group and state arenas.
 
-Group ``g`` owns two tensors ``[runs_in_group, pages, kv_heads, page_size,
+Group ``g`` owns two tensors (one, where the values are a part of the key rows) ``[runs_in_group, pages, kv_heads, page_size,
 head_dim]`` (keys, and values, whose last size may differ) in the storage dtype: the keys of one kv head in one
 page are contiguous, so a kernel that serves one kv head reads whole runs of
 memory.  Token ``p`` of a request lies in page ``block_table[p // page_size]``
@@ -41,7 +41,7 @@ def group_runs(needs: list, cache_from: list) -> tuple[list[CacheGroup], dict[in
             where[run] = (len(groups) - 1, 0)
     groups = [CacheGroup(tuple(m), n.num_kv_heads, n.head_dim, n.window,
                          None if n.value_size == n.head_dim else n.value_size,
-                         n.keep_first if n.window is not None else 0)
+                         n.keep_first if n.window is not None else 0, n.value_offset)
               for n, m in zip(groups, members)]
     for run, source in enumerate(cache_from):
         if source is None:
@@ -58,7 +58,8 @@ def group_runs(needs: list, cache_from: list) -> tuple[list[CacheGroup], dict[in
 
 
 def bytes_per_page(group: CacheGroup, page_size: int, itemsize: int) -> int:
-    return len(group.runs) * page_size * group.num_kv_heads * (group.head_dim + group.value_size) * itemsize
+    stored = group.head_dim + (group.value_size if group.value_offset is None else 0)
+    return len(group.runs) * page_size * group.num_kv_heads * stored * itemsize
 
 
 class CacheStorage:
@@ -76,7 +77,12 @@ class CacheStorage:
         for group, pages in zip(self.groups, self.pages_per_group):
             shape = (len(group.runs), pages, group.num_kv_heads, page_size)
             self.keys.append(torch.zeros(shape + (group.head_dim,), dtype=dtype, device=device))
-            self.values.append(torch.zeros(shape + (group.value_size,), dtype=dtype, device=device))
+            if group.value_offset is None:
+                self.values.append(torch.zeros(shape + (group.value_size,), dtype=dtype, device=device))
+            else:       # values are read out of the key rows
+                if not 0 <= group.value_offset <= group.head_dim - group.value_size:
+                    raise ValueError("values inside the key rows must fit them")
+                self.values.append(None)
         self.state: dict[int, torch.Tensor] = {}
         for run, need in enumerate(needs):
             if isinstance(need, StateNeed):
@@ -89,7 +95,8 @@ class CacheStorage:
     def kv_of(self, run: int) -> tuple[torch.Tensor, torch.Tensor]:
         """Keys and values ``[pages, kv_heads, page_size, head_dim]`` of one run."""
         group, index = self.where[run]
-        return self.keys[group][index], self.values[group][index]
+        values = self.values[group]
+        return self.keys[group][index], None if values is None else values[index]
 
     def state_of(self, run: int) -> torch.Tensor:
         return self.state[run]

@@ -24,22 +24,25 @@
 
 #define ATTN_CHUNK 256
 #define ATTN_MAX_DIMS 8      // head_dim <= 256: lane l owns dims l, l + 32, ...
+#define ATTN_WIDE_DIMS 20    // the wide form: keys and values up to 640
 #define ATTN_WARPS 4
 
+template <int DIMS>
 struct Partial {
     float max, sum;
-    float out[ATTN_MAX_DIMS];
+    float out[DIMS];
 };
 
 // running (M, L, O) <- merge with a chunk's (m, l, o); explicit operations so that
 // both callers compile to the same arithmetic.
-__device__ __forceinline__ void merge_partial(Partial& total, const Partial& part) {
+template <int DIMS>
+__device__ __forceinline__ void merge_partial(Partial<DIMS>& total, const Partial<DIMS>& part) {
     const float new_max = fmaxf(total.max, part.max);
     const float scale_total = total.max == -INFINITY ? 0.0f : expf(__fsub_rn(total.max, new_max));
     const float scale_part = part.max == -INFINITY ? 0.0f : expf(__fsub_rn(part.max, new_max));
     total.sum = __fadd_rn(__fmul_rn(total.sum, scale_total), __fmul_rn(part.sum, scale_part));
 #pragma unroll
-    for (int i = 0; i < ATTN_MAX_DIMS; ++i)
+    for (int i = 0; i < DIMS; ++i)
         total.out[i] = __fadd_rn(__fmul_rn(total.out[i], scale_total), __fmul_rn(part.out[i], scale_part));
     total.max = new_max;
 }
@@ -91,15 +94,18 @@ __device__ __forceinline__ float dot_head<bf16>(const float* __restrict__ q_shar
 }
 
 // One chunk of keys [first, last] (inclusive, inside one ATTN_CHUNK block) for one row.
-template <typename T>
+// `slope` > 0 takes slope * (position - j) off the score of key j; `value_stride`: elements from one
+// slot's value to the next (values may be a part of the key rows).
+template <typename T, int DIMS>
 __device__ __forceinline__ void attend_chunk(
-    Partial& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
+    Partial<DIMS>& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
     const T* __restrict__ value_cache, const int* __restrict__ table, int first, int last,
-    int kv_head, int num_kv, int head_dim, int value_dim, int page_size, float scale, int lane) {
+    int kv_head, int num_kv, int head_dim, int value_dim, int64_t value_stride, int page_size, float scale,
+    float slope, int position, int lane) {
     part.max = -INFINITY;
     part.sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < ATTN_MAX_DIMS; ++i) part.out[i] = 0.0f;
+    for (int i = 0; i < DIMS; ++i) part.out[i] = 0.0f;
     for (int base = first - first % 32; base <= last; base += 32) {
         const int j = base + lane;
         const bool valid = j >= first && j <= last;
@@ -109,6 +115,7 @@ __device__ __forceinline__ void attend_chunk(
             slot = ((int64_t)table[j / page_size] * num_kv + kv_head) * page_size + j % page_size;
             const T* k = key_cache + slot * head_dim;
             score = __fmul_rn(dot_head<T>(q_shared, k, head_dim), scale);
+            if (slope != 0.0f) score = __fsub_rn(score, __fmul_rn(slope, (float)(position - j)));
         }
         const float tile_max = warp_max(score);          // at least one key of a tile is valid
         const float new_max = fmaxf(part.max, tile_max);
@@ -116,14 +123,14 @@ __device__ __forceinline__ void attend_chunk(
         const float p = valid ? expf(__fsub_rn(score, new_max)) : 0.0f;
         part.sum = __fadd_rn(__fmul_rn(part.sum, rescale), warp_sum(p));
 #pragma unroll
-        for (int i = 0; i < ATTN_MAX_DIMS; ++i) part.out[i] = __fmul_rn(part.out[i], rescale);
+        for (int i = 0; i < DIMS; ++i) part.out[i] = __fmul_rn(part.out[i], rescale);
         const int count = min(32, last - base + 1);
         for (int jj = max(0, first - base); jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int64_t sj = __shfl_sync(0xffffffffu, slot, jj);
-            const T* v = value_cache + sj * value_dim;
+            const T* v = value_cache + sj * value_stride;
 #pragma unroll
-            for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
+            for (int i = 0; i < DIMS; ++i) {
                 const int dim = lane + 32 * i;
                 if (dim < value_dim) part.out[i] = __fmaf_rn(pj, to_float<T>(v[dim]), part.out[i]);
             }
@@ -135,26 +142,27 @@ __device__ __forceinline__ void attend_chunk(
 // Everything of chunk `chunk` that the query at `position` sees: the kept first keys that fall
 // into the chunk (they lie before lo), then the keys of the window.  Both pieces start from an
 // empty partial and are merged in this order, whoever calls.
-template <typename T>
+template <typename T, int DIMS>
 __device__ __forceinline__ void attend_visible(
-    Partial& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
+    Partial<DIMS>& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
     const T* __restrict__ value_cache, const int* __restrict__ table, int chunk, int lo, int kept, int position,
-    int kv_head, int num_kv, int head_dim, int value_dim, int page_size, float scale, int lane) {
+    int kv_head, int num_kv, int head_dim, int value_dim, int64_t value_stride, int page_size, float scale,
+    float slope, int lane) {
     const int begin = chunk * ATTN_CHUNK, end = begin + ATTN_CHUNK - 1;
     const int first = max(lo, begin), last = min(position, end);
     if (kept > begin) {                                   // kept = min(keep_first, lo): keys 0..kept-1
-        attend_chunk<T>(part, q_shared, key_cache, value_cache, table, begin, min(kept - 1, end), kv_head,
-                        num_kv, head_dim, value_dim, page_size, scale, lane);
+        attend_chunk<T, DIMS>(part, q_shared, key_cache, value_cache, table, begin, min(kept - 1, end), kv_head,
+                              num_kv, head_dim, value_dim, value_stride, page_size, scale, slope, position, lane);
         if (first <= last) {
-            Partial more;
-            attend_chunk<T>(more, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv,
-                            head_dim, value_dim, page_size, scale, lane);
+            Partial<DIMS> more;
+            attend_chunk<T, DIMS>(more, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv,
+                                  head_dim, value_dim, value_stride, page_size, scale, slope, position, lane);
             merge_partial(part, more);
         }
         return;
     }
-    attend_chunk<T>(part, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv, head_dim,
-                    value_dim, page_size, scale, lane);
+    attend_chunk<T, DIMS>(part, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv, head_dim,
+                          value_dim, value_stride, page_size, scale, slope, position, lane);
 }
 
 // Whether the query sees anything of a chunk.
@@ -165,17 +173,56 @@ __device__ __forceinline__ bool chunk_visible(int chunk, int lo, int kept, int p
 
 __device__ __forceinline__ float gate_of(float g) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g))); }
 
+// What the rows of one launch share beyond the sizes: `slopes` (one float a query head, or null):
+// slope * (position - j) is taken off the score of key j; `sinks` (one float a query head, or null):
+// exp(sink) joins the softmax's denominator once, with no key and no value; `gate_per_head`: the
+// gate holds one number a head instead of one a value.
+struct RowExtras {
+    const float* slopes;
+    const float* sinks;
+    int gate_per_head;
+    int64_t value_stride;
+};
+
+// (M, L, O) of a finished row -> output: the sink joins the denominator, then division, gate, rounding.
+template <typename T, int DIMS>
+__device__ __forceinline__ void finish_row(Partial<DIMS>& total, const float* sinks, int head, const T* gate,
+                                           int64_t gate_token_stride, int gate_per_head, int token, T* out_row,
+                                           int value_dim, int lane) {
+    float keep = 1.0f;
+    if (sinks) {
+        const float sink = sinks[head];
+        const float top = fmaxf(total.max, sink);
+        keep = expf(__fsub_rn(total.max, top));
+        total.sum = __fadd_rn(__fmul_rn(total.sum, keep), expf(__fsub_rn(sink, top)));
+    }
+    const T* gate_row = nullptr;
+    float head_gate = 1.0f;
+    if (gate && gate_per_head) head_gate = gate_of(to_float<T>(gate[(int64_t)token * gate_token_stride + head]));
+    else if (gate) gate_row = gate + (int64_t)token * gate_token_stride + (int64_t)head * value_dim;
+#pragma unroll
+    for (int i = 0; i < DIMS; ++i) {
+        const int dim = lane + 32 * i;
+        if (dim < value_dim) {
+            float o = sinks ? __fdiv_rn(__fmul_rn(total.out[i], keep), total.sum) : __fdiv_rn(total.out[i], total.sum);
+            if (gate_row) o = __fmul_rn(o, gate_of(to_float<T>(gate_row[dim])));
+            else if (gate) o = __fmul_rn(o, head_gate);
+            out_row[dim] = from_float<T>(o);
+        }
+    }
+}
+
 // mode rows: grid.x covers (token, head) rows, grid.y = 1, each warp walks all chunks.
 // mode split: grid.y = chunk index; partials go to scratch.
-template <typename T, bool SPLIT>
+template <typename T, bool SPLIT, int DIMS>
 __global__ void paged_attention_rows_kernel(
     const T* __restrict__ q, int64_t q_token_stride, const T* __restrict__ key_cache,
     const T* __restrict__ value_cache, const int* __restrict__ block_tables, int table_stride,
     const int* __restrict__ token_row, const int* __restrict__ positions, T* __restrict__ out,
     int64_t out_token_stride, const T* gate, int64_t gate_token_stride,
     float* __restrict__ scratch, int max_chunks, int tokens, int num_q, int num_kv, int head_dim,
-    int value_dim, int page_size, int window, int keep_first, float scale) {
-    __shared__ float q_shared[ATTN_WARPS][256];
+    int value_dim, int page_size, int window, int keep_first, float scale, RowExtras extras) {
+    __shared__ float q_shared[ATTN_WARPS][DIMS * 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * ATTN_WARPS + warp;
     if (row >= (int64_t)tokens * num_q) return;
@@ -197,51 +244,47 @@ __global__ void paged_attention_rows_kernel(
     __syncwarp();
     const int* table = block_tables + (int64_t)request * table_stride;
     const int kv_head = head / (num_q / num_kv);
+    const float slope = extras.slopes ? extras.slopes[head] : 0.0f;
 
     if (SPLIT) {
         const int chunk = blockIdx.y;
-        Partial part;
-        attend_visible<T>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
-                          kv_head, num_kv, head_dim, value_dim, page_size, scale, lane);
+        Partial<DIMS> part;
+        attend_visible<T, DIMS>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
+                                kv_head, num_kv, head_dim, value_dim, extras.value_stride, page_size, scale, slope,
+                                lane);
         float* dst = scratch + (row * max_chunks + chunk) * (int64_t)(value_dim + 2);
         if (lane == 0) { dst[0] = part.max; dst[1] = part.sum; }
 #pragma unroll
-        for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
+        for (int i = 0; i < DIMS; ++i) {
             const int dim = lane + 32 * i;
             if (dim < value_dim) dst[2 + dim] = part.out[i];
         }
     } else {
-        Partial total;
+        Partial<DIMS> total;
         total.max = -INFINITY;
         total.sum = 0.0f;
 #pragma unroll
-        for (int i = 0; i < ATTN_MAX_DIMS; ++i) total.out[i] = 0.0f;
+        for (int i = 0; i < DIMS; ++i) total.out[i] = 0.0f;
         for (int chunk = 0; chunk <= last_chunk; ++chunk) {
             if (!chunk_visible(chunk, lo, kept, position)) continue;
-            Partial part;
-            attend_visible<T>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
-                              kv_head, num_kv, head_dim, value_dim, page_size, scale, lane);
+            Partial<DIMS> part;
+            attend_visible<T, DIMS>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
+                                    kv_head, num_kv, head_dim, value_dim, extras.value_stride, page_size, scale,
+                                    slope, lane);
             merge_partial(total, part);
         }
-        const T* gate_row = gate ? gate + (int64_t)token * gate_token_stride + (int64_t)head * value_dim : nullptr;
-#pragma unroll
-        for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
-            const int dim = lane + 32 * i;
-            if (dim < value_dim) {
-                float o = __fdiv_rn(total.out[i], total.sum);
-                if (gate_row) o = __fmul_rn(o, gate_of(to_float<T>(gate_row[dim])));
-                out_row[dim] = from_float<T>(o);
-            }
-        }
+        finish_row<T, DIMS>(total, extras.sinks, head, gate, gate_token_stride, extras.gate_per_head, token,
+                            out_row, value_dim, lane);
     }
 }
 
-template <typename T>
+template <typename T, int DIMS>
 __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, int max_chunks,
                                             const int* __restrict__ token_row,
                                             const int* __restrict__ positions, T* __restrict__ out,
                                             int64_t out_token_stride, const T* gate, int64_t gate_token_stride,
-                                            int tokens, int num_q, int head_dim, int window, int keep_first) {
+                                            int tokens, int num_q, int head_dim, int window, int keep_first,
+                                            RowExtras extras) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * ATTN_WARPS + warp;
     if (row >= (int64_t)tokens * num_q) return;
@@ -251,11 +294,11 @@ __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, i
     const int lo = window > 0 ? max(0, position - window + 1) : 0;
     const int kept = min(keep_first, lo);
     T* out_row = out + (int64_t)token * out_token_stride + (int64_t)head * head_dim;
-    Partial total;
+    Partial<DIMS> total;
     total.max = -INFINITY;
     total.sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < ATTN_MAX_DIMS; ++i) total.out[i] = 0.0f;
+    for (int i = 0; i < DIMS; ++i) total.out[i] = 0.0f;
     // The scratch holds max_chunks partials a row.  A caller whose max_chunks is too small for this
     // row's position gets the row as NaN: the first kernel wrote no partial beyond max_chunks - 1,
     // and reading on would take the next row's (or leave the buffer).
@@ -268,26 +311,18 @@ __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, i
     for (int chunk = 0; chunk <= last_chunk; ++chunk) {
         if (!chunk_visible(chunk, lo, kept, position)) continue;
         const float* src = scratch + (row * max_chunks + chunk) * (int64_t)(head_dim + 2);
-        Partial part;
+        Partial<DIMS> part;
         part.max = src[0];
         part.sum = src[1];
 #pragma unroll
-        for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
+        for (int i = 0; i < DIMS; ++i) {
             const int dim = lane + 32 * i;
             part.out[i] = dim < head_dim ? src[2 + dim] : 0.0f;
         }
         merge_partial(total, part);
     }
-    const T* gate_row = gate ? gate + (int64_t)token * gate_token_stride + (int64_t)head * head_dim : nullptr;
-#pragma unroll
-    for (int i = 0; i < ATTN_MAX_DIMS; ++i) {
-        const int dim = lane + 32 * i;
-        if (dim < head_dim) {
-            float o = __fdiv_rn(total.out[i], total.sum);
-            if (gate_row) o = __fmul_rn(o, gate_of(to_float<T>(gate_row[dim])));
-            out_row[dim] = from_float<T>(o);
-        }
-    }
+    finish_row<T, DIMS>(total, extras.sinks, head, gate, gate_token_stride, extras.gate_per_head, token, out_row,
+                        head_dim, lane);
 }
 
 extern "C" int tvb_attention_chunk_keys() { return ATTN_CHUNK; }
@@ -297,24 +332,51 @@ extern "C" long long tvb_attention_rows_scratch_floats(int tokens, int num_q, in
     return (long long)tokens * num_q * max_chunks * (head_dim + 2);
 }
 
+template <typename T, int DIMS>
+static void launch_rows(const void* q, long long q_token_stride, const void* key_cache, const void* value_cache,
+                        const int* block_tables, int table_stride, const int* token_row, const int* positions,
+                        void* out, long long out_token_stride, const void* gate, long long gate_token_stride,
+                        float* scratch, int max_chunks, int tokens, int num_q, int num_kv, int head_dim,
+                        int value_dim, int page_size, int window, int keep_first, float scale, RowExtras extras,
+                        unsigned blocks, cudaStream_t s) {
+    dim3 grid(blocks, max_chunks > 0 ? max_chunks : 1);
+    if (max_chunks > 0) {
+        paged_attention_rows_kernel<T, true, DIMS><<<grid, ATTN_WARPS * 32, 0, s>>>(
+            (const T*)q, q_token_stride, (const T*)key_cache, (const T*)value_cache, block_tables, table_stride,
+            token_row, positions, (T*)out, out_token_stride, (const T*)gate, gate_token_stride, scratch, max_chunks,
+            tokens, num_q, num_kv, head_dim, value_dim, page_size, window, keep_first, scale, extras);
+        merge_attention_rows_kernel<T, DIMS><<<blocks, ATTN_WARPS * 32, 0, s>>>(
+            scratch, max_chunks, token_row, positions, (T*)out, out_token_stride, (const T*)gate, gate_token_stride,
+            tokens, num_q, value_dim, window, keep_first, extras);
+    } else {
+        paged_attention_rows_kernel<T, false, DIMS><<<grid, ATTN_WARPS * 32, 0, s>>>(
+            (const T*)q, q_token_stride, (const T*)key_cache, (const T*)value_cache, block_tables, table_stride,
+            token_row, positions, (T*)out, out_token_stride, (const T*)gate, gate_token_stride, scratch, max_chunks,
+            tokens, num_q, num_kv, head_dim, value_dim, page_size, window, keep_first, scale, extras);
+    }
+}
+
 // max_chunks = 0 selects mode rows (no scratch).  Otherwise max_chunks must be at
 // least ceil((largest position + 1) / ATTN_CHUNK) of the batch and scratch must hold
-// tokens * num_q * max_chunks * (head_dim + 2) floats.  The host cannot see the positions:
+// tokens * num_q * max_chunks * (value_dim + 2) floats.  The host cannot see the positions:
 // a row whose position needs more chunks than max_chunks is written as NaN (and nothing
 // outside the stated scratch is read or written).
-// The general form: keys `head_dim` and values `value_dim` wide, the first `keep_first` keys seen
-// from behind a window, output rows `out_token_stride` apart, an optional gate with a stride of
-// its own.  Scratch of the split mode: tokens * num_q * max_chunks * (value_dim + 2) floats.
-extern "C" int tvb_attention_rows_general(const void* q, long long q_token_stride, const void* key_cache,
-                                          const void* value_cache, const int* block_tables, int table_stride,
-                                          const int* token_row, const int* positions, void* out,
-                                          long long out_token_stride, const void* gate, long long gate_token_stride,
-                                          float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
-                                          int head_dim, int value_dim, int page_size, int window, int keep_first,
-                                          float scale, int dtype, void* stream) {
+// The widest form: keys `head_dim` and values `value_dim` wide (up to 640), the first `keep_first`
+// keys seen from behind a window, output rows `out_token_stride` apart, an optional gate with a stride
+// of its own, one number a value or (`gate_per_head`) one a head, a distance bias (`slopes`), a sink in
+// the denominator (`sinks`), and values that lie `value_stride` elements apart (0: value_dim), which
+// lets them be a part of the key rows.
+extern "C" int tvb_attention_rows_biased(const void* q, long long q_token_stride, const void* key_cache,
+                                         const void* value_cache, long long value_stride, const int* block_tables,
+                                         int table_stride, const int* token_row, const int* positions, void* out,
+                                         long long out_token_stride, const void* gate, long long gate_token_stride,
+                                         int gate_per_head, const float* slopes, const float* sinks,
+                                         float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
+                                         int head_dim, int value_dim, int page_size, int window, int keep_first,
+                                         float scale, int dtype, void* stream) {
     if (tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim > 32 * ATTN_MAX_DIMS || value_dim <= 0 || value_dim > 32 * ATTN_MAX_DIMS ||
-        num_q <= 0 || num_kv <= 0 || keep_first < 0 ||
+    if (head_dim <= 0 || head_dim > 32 * ATTN_WIDE_DIMS || value_dim <= 0 || value_dim > 32 * ATTN_WIDE_DIMS ||
+        num_q <= 0 || num_kv <= 0 || keep_first < 0 || value_stride < 0 ||
         num_q % num_kv || page_size <= 0 || max_chunks < 0 || max_chunks > 65535 ||
         (max_chunks > 0 && !scratch))
         return TVB_BAD_ARGUMENT;
@@ -322,31 +384,32 @@ extern "C" int tvb_attention_rows_general(const void* q, long long q_token_strid
     const int64_t blocks = (rows + ATTN_WARPS - 1) / ATTN_WARPS;
     if (blocks > 2147483647LL) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((unsigned)blocks, max_chunks > 0 ? max_chunks : 1);
-#define LAUNCH_ROWS(T)                                                                              \
-    do {                                                                                            \
-        if (max_chunks > 0) {                                                                       \
-            paged_attention_rows_kernel<T, true><<<grid, ATTN_WARPS * 32, 0, s>>>(                  \
-                (const T*)q, q_token_stride, (const T*)key_cache, (const T*)value_cache,            \
-                block_tables, table_stride, token_row, positions, (T*)out, out_token_stride,        \
-                (const T*)gate, gate_token_stride, scratch, max_chunks,                             \
-                tokens, num_q, num_kv, head_dim, value_dim, page_size, window, keep_first, scale);  \
-            merge_attention_rows_kernel<T><<<(unsigned)blocks, ATTN_WARPS * 32, 0, s>>>(            \
-                scratch, max_chunks, token_row, positions, (T*)out, out_token_stride,               \
-                (const T*)gate, gate_token_stride, tokens, num_q, value_dim, window, keep_first);   \
-        } else {                                                                                    \
-            paged_attention_rows_kernel<T, false><<<grid, ATTN_WARPS * 32, 0, s>>>(                 \
-                (const T*)q, q_token_stride, (const T*)key_cache, (const T*)value_cache,            \
-                block_tables, table_stride, token_row, positions, (T*)out, out_token_stride,        \
-                (const T*)gate, gate_token_stride, scratch, max_chunks,                             \
-                tokens, num_q, num_kv, head_dim, value_dim, page_size, window, keep_first, scale);  \
-        }                                                                                           \
-    } while (0)
-    if (dtype == TVB_F32) LAUNCH_ROWS(float);
-    else if (dtype == TVB_BF16) LAUNCH_ROWS(bf16);
+    RowExtras extras{slopes, sinks, gate_per_head, value_stride > 0 ? value_stride : value_dim};
+    const bool wide = head_dim > 32 * ATTN_MAX_DIMS || value_dim > 32 * ATTN_MAX_DIMS;
+#define LAUNCH_ROWS(T, DIMS)                                                                             \
+    launch_rows<T, DIMS>(q, q_token_stride, key_cache, value_cache, block_tables, table_stride, token_row, \
+                         positions, out, out_token_stride, gate, gate_token_stride, scratch, max_chunks,   \
+                         tokens, num_q, num_kv, head_dim, value_dim, page_size, window, keep_first, scale, \
+                         extras, (unsigned)blocks, s)
+    if (dtype == TVB_F32) { if (wide) LAUNCH_ROWS(float, ATTN_WIDE_DIMS); else LAUNCH_ROWS(float, ATTN_MAX_DIMS); }
+    else if (dtype == TVB_BF16) { if (wide) LAUNCH_ROWS(bf16, ATTN_WIDE_DIMS); else LAUNCH_ROWS(bf16, ATTN_MAX_DIMS); }
     else return TVB_BAD_ARGUMENT;
 #undef LAUNCH_ROWS
     return tvb_last_error();
+}
+
+extern "C" int tvb_attention_rows_general(const void* q, long long q_token_stride, const void* key_cache,
+                                          const void* value_cache, const int* block_tables, int table_stride,
+                                          const int* token_row, const int* positions, void* out,
+                                          long long out_token_stride, const void* gate, long long gate_token_stride,
+                                          float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
+                                          int head_dim, int value_dim, int page_size, int window, int keep_first,
+                                          float scale, int dtype, void* stream) {
+    if (head_dim > 32 * ATTN_MAX_DIMS || value_dim > 32 * ATTN_MAX_DIMS) return TVB_BAD_ARGUMENT;
+    return tvb_attention_rows_biased(q, q_token_stride, key_cache, value_cache, 0, block_tables, table_stride,
+                                     token_row, positions, out, out_token_stride, gate, gate_token_stride, 0,
+                                     nullptr, nullptr, scratch, max_chunks, tokens, num_q, num_kv, head_dim,
+                                     value_dim, page_size, window, keep_first, scale, dtype, stream);
 }
 
 extern "C" int tvb_attention_rows(const void* q, long long q_token_stride, const void* key_cache,

@@ -1,0 +1,268 @@
+// Pointwise steps around attention whose queries, keys and values come through low-rank latents,
+// and around attention that normalises whole projections.  All arithmetic float32, one rounding
+// to the storage type where a result is stored.
+//
+//   projection_norm   in place on segments of a packed projection row: v * rsqrt(mean(v^2) + eps) * w
+//                     over the whole segment (all heads at once, weight of the segment's size), and,
+//                     for segments that ask for it, times the query temperature
+//                     1 + coef * ln(floor((p + 1) / every) + 1) of the token's position p
+//   latent_prepare    from a packed projection row [.. dq .. | .. dkv ..]: the query latent
+//                     RMSnorm(dq) * w_q to a buffer; the key/value latent RMSnorm(dkv[:rank]) * w_kv and
+//                     the rotated rest of dkv side by side, [latent | rotated], to the token's cache slot
+//   rotate_heads      pairs (2i, 2i + 1) of a slice of every head turned by position * inv_freq[i],
+//                     cosine and sine times `magnitude`, from one strided layout to another
+//   head_product      out[t, h, j] = sum_k x[t, h, k] * w[h, j, k], optionally times sigmoid(gate[t, h, j]):
+//                     one small product a head (the up-projections of latent attention, folded into the
+//                     query and applied to the attended latents)
+#include "common.cuh"
+
+// ------------------------------------------------------------ projection_norm
+struct NormSegment {
+    int at, cols;
+    const void* weight;
+    int tempered;
+};
+
+template <typename T, typename W>
+__global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment first, NormSegment second,
+                                       const int* __restrict__ positions, float eps, float coef, int every) {
+    __shared__ float scratch[32];
+    const NormSegment seg = blockIdx.y == 0 ? first : second;
+    T* row = proj + (int64_t)blockIdx.x * stride + seg.at;
+    const W* weight = (const W*)seg.weight;
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
+        const float v = to_float<T>(row[i]);
+        part = __fmaf_rn(v, v, part);
+    }
+    const float total = block_sum(part, scratch);
+    const float inverse = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)seg.cols), eps)));
+    float temperature = 1.0f;
+    if (seg.tempered && every > 0) {
+        const int p = max(positions[blockIdx.x], 0);
+        temperature = __fmaf_rn(coef, logf((float)((p + 1) / every + 1)), 1.0f);
+    }
+    for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
+        float o = __fmul_rn(__fmul_rn(to_float<T>(row[i]), inverse), to_float<W>(weight[i]));
+        if (seg.tempered) o = __fmul_rn(o, temperature);
+        row[i] = from_float<T>(o);
+    }
+}
+
+// Two segments a launch (queries and keys); `second_cols` = 0 leaves the second out.
+extern "C" int tvb_projection_norm(void* proj, long long stride, int first_at, int first_cols,
+                                   const void* first_weight, int first_tempered, int second_at, int second_cols,
+                                   const void* second_weight, int second_tempered, int weight_dtype,
+                                   const int* positions, float eps, float coef, int every, int tokens, int dtype,
+                                   void* stream) {
+    if (tokens <= 0) return 0;
+    if (first_cols <= 0 || second_cols < 0 || !first_weight || (second_cols > 0 && !second_weight) ||
+        ((first_tempered || second_tempered) && every > 0 && !positions))
+        return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    NormSegment first{first_at, first_cols, first_weight, first_tempered};
+    NormSegment second{second_at, second_cols, second_weight, second_tempered};
+    const int widest = first_cols > second_cols ? first_cols : second_cols;
+    const int threads = widest >= 2048 ? 512 : (widest >= 512 ? 256 : 128);
+    for (int start = 0; start < tokens; start += 65535) {      // grid.x carries the tokens
+        const int count = tokens - start < 65535 ? tokens - start : 65535;
+        dim3 grid(count, second_cols > 0 ? 2 : 1);
+        const int* p = positions ? positions + start : nullptr;
+#define GO(T, W) projection_norm_kernel<T, W><<<grid, threads, 0, s>>>((T*)proj + (int64_t)start * stride, stride, \
+                                                                        first, second, p, eps, coef, every)
+        if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float);
+        else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) GO(bf16, bf16);
+        else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float);
+        else return TVB_BAD_ARGUMENT;
+#undef GO
+    }
+    return tvb_last_error();
+}
+
+// ------------------------------------------------------------- latent_prepare
+__device__ __forceinline__ void turn_pair(float u, float v, float angle, float magnitude, float& a, float& b) {
+    float sine, cosine;
+    sincosf(angle, &sine, &cosine);
+    sine = __fmul_rn(sine, magnitude);
+    cosine = __fmul_rn(cosine, magnitude);
+    a = __fsub_rn(__fmul_rn(u, cosine), __fmul_rn(v, sine));
+    b = __fadd_rn(__fmul_rn(v, cosine), __fmul_rn(u, sine));
+}
+
+template <typename T, typename W>
+__global__ void latent_prepare_kernel(const T* proj, int64_t stride, int dq_at, int q_rank, const W* __restrict__ q_weight,
+                                      T* __restrict__ q_latent, int64_t q_latent_stride, int dkv_at, int kv_rank,
+                                      const W* __restrict__ kv_weight, int rot_dim, const float* __restrict__ inv_freq,
+                                      float magnitude, const int* __restrict__ positions,
+                                      const int* __restrict__ slots, T* __restrict__ cache, float eps) {
+    __shared__ float scratch[32];
+    const int token = blockIdx.x;
+    const T* row = proj + (int64_t)token * stride;
+    if (q_rank > 0) {
+        float part = 0.0f;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+            const float v = to_float<T>(row[dq_at + i]);
+            part = __fmaf_rn(v, v, part);
+        }
+        const float total = block_sum(part, scratch);
+        const float inverse = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)q_rank), eps)));
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+            q_latent[(int64_t)token * q_latent_stride + i] =
+                from_float<T>(__fmul_rn(__fmul_rn(to_float<T>(row[dq_at + i]), inverse), to_float<W>(q_weight[i])));
+    }
+    const int slot = slots ? slots[token] : -1;
+    if (slot < 0) return;                       // this run writes no cache, or a padding row
+    T* dst = cache + (int64_t)slot * (kv_rank + rot_dim);
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
+        const float v = to_float<T>(row[dkv_at + i]);
+        part = __fmaf_rn(v, v, part);
+    }
+    const float total = block_sum(part, scratch);
+    const float inverse = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)kv_rank), eps)));
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x)
+        dst[i] = from_float<T>(__fmul_rn(__fmul_rn(to_float<T>(row[dkv_at + i]), inverse), to_float<W>(kv_weight[i])));
+    const float position = (float)positions[token];
+    for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x) {
+        float a, b;
+        turn_pair(to_float<T>(row[dkv_at + kv_rank + 2 * i]), to_float<T>(row[dkv_at + kv_rank + 2 * i + 1]),
+                  __fmul_rn(position, inv_freq[i]), magnitude, a, b);
+        dst[kv_rank + 2 * i] = from_float<T>(a);
+        dst[kv_rank + 2 * i + 1] = from_float<T>(b);
+    }
+}
+
+// `cache`: rows of kv_rank + rot_dim per slot (one kv head); `slots` may be null (nothing is cached).
+extern "C" int tvb_latent_prepare(const void* proj, long long stride, int dq_at, int q_rank, const void* q_weight,
+                                  void* q_latent, long long q_latent_stride, int dkv_at, int kv_rank,
+                                  const void* kv_weight, int weight_dtype, int rot_dim, const float* inv_freq,
+                                  float magnitude, const int* positions, const int* slots, void* cache, float eps,
+                                  int tokens, int dtype, void* stream) {
+    if (tokens <= 0) return 0;
+    if (q_rank < 0 || kv_rank <= 0 || rot_dim < 0 || rot_dim % 2 || !kv_weight || !positions ||
+        (q_rank > 0 && (!q_weight || !q_latent)) || (rot_dim > 0 && !inv_freq) || (slots && !cache))
+        return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int widest = q_rank > kv_rank ? q_rank : kv_rank;
+    const int threads = widest >= 1024 ? 256 : (widest >= 256 ? 128 : 64);
+#define GO(T, W) latent_prepare_kernel<T, W><<<tokens, threads, 0, s>>>(                                        \
+        (const T*)proj, stride, dq_at, q_rank, (const W*)q_weight, (T*)q_latent, q_latent_stride, dkv_at,      \
+        kv_rank, (const W*)kv_weight, rot_dim, inv_freq, magnitude, positions, slots, (T*)cache, eps)
+    if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float);
+    else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) GO(bf16, bf16);
+    else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float);
+    else return TVB_BAD_ARGUMENT;
+#undef GO
+    return tvb_last_error();
+}
+
+// --------------------------------------------------------------- rotate_heads
+template <typename T>
+__global__ void rotate_heads_kernel(const T* src, int64_t src_token_stride, int64_t src_head_stride, T* dst,
+                                    int64_t dst_token_stride, int64_t dst_head_stride, int heads, int rot_dim,
+                                    const float* __restrict__ inv_freq, float magnitude,
+                                    const int* __restrict__ positions, int64_t pairs) {
+    const int64_t index = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= pairs) return;
+    const int half = rot_dim / 2;
+    const int i = (int)(index % half);
+    const int head = (int)((index / half) % heads);
+    const int64_t token = index / ((int64_t)half * heads);
+    const T* from = src + token * src_token_stride + head * src_head_stride + 2 * i;
+    T* to = dst + token * dst_token_stride + head * dst_head_stride + 2 * i;
+    float a, b;
+    turn_pair(to_float<T>(from[0]), to_float<T>(from[1]), __fmul_rn((float)max(positions[token], 0), inv_freq[i]),
+              magnitude, a, b);
+    to[0] = from_float<T>(a);
+    to[1] = from_float<T>(b);
+}
+
+extern "C" int tvb_rotate_heads(const void* src, long long src_token_stride, long long src_head_stride, void* dst,
+                                long long dst_token_stride, long long dst_head_stride, int heads, int rot_dim,
+                                const float* inv_freq, float magnitude, const int* positions, int tokens, int dtype,
+                                void* stream) {
+    if (tokens <= 0 || rot_dim == 0) return 0;
+    if (heads <= 0 || rot_dim < 0 || rot_dim % 2 || !inv_freq || !positions) return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t pairs = (int64_t)tokens * heads * (rot_dim / 2);
+    const int64_t blocks = (pairs + 255) / 256;
+    if (blocks > 2147483647LL) return TVB_BAD_ARGUMENT;
+#define GO(T) rotate_heads_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(                                          \
+        (const T*)src, src_token_stride, src_head_stride, (T*)dst, dst_token_stride, dst_head_stride, heads,    \
+        rot_dim, inv_freq, magnitude, positions, pairs)
+    if (dtype == TVB_F32) GO(float);
+    else if (dtype == TVB_BF16) GO(bf16);
+    else return TVB_BAD_ARGUMENT;
+#undef GO
+    return tvb_last_error();
+}
+
+// --------------------------------------------------------------- head_product
+// A block serves HP_TOKENS tokens of one head: their x rows wait in shared memory as float32, every
+// warp takes output columns in turn, its lanes share the k of a weight row (coalesced) and the sums
+// meet by shuffles.  The order of additions depends on k alone.
+#define HP_TOKENS 8
+#define HP_WARPS 8
+
+template <typename T>
+__global__ void head_product_kernel(const T* x, int64_t x_token_stride, int64_t x_head_stride,
+                                    const T* __restrict__ w, T* out, int64_t out_token_stride,
+                                    int64_t out_head_stride, const T* gate, int64_t gate_token_stride, int tokens,
+                                    int n, int k) {
+    extern __shared__ float x_rows[];                  // [HP_TOKENS][k]
+    const int head = blockIdx.y;
+    const int first = blockIdx.x * HP_TOKENS;
+    const int count = min(HP_TOKENS, tokens - first);
+    for (int i = threadIdx.x; i < HP_TOKENS * k; i += blockDim.x) {
+        const int t = i / k, c = i % k;
+        x_rows[i] = t < count ? to_float<T>(x[(int64_t)(first + t) * x_token_stride + head * x_head_stride + c]) : 0.0f;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* w_head = w + (int64_t)head * n * k;
+    for (int j = warp; j < n; j += HP_WARPS) {
+        const T* w_row = w_head + (int64_t)j * k;
+        float sums[HP_TOKENS];
+#pragma unroll
+        for (int t = 0; t < HP_TOKENS; ++t) sums[t] = 0.0f;
+        for (int c = lane; c < k; c += 32) {
+            const float wv = to_float<T>(w_row[c]);
+#pragma unroll
+            for (int t = 0; t < HP_TOKENS; ++t) sums[t] = __fmaf_rn(x_rows[t * k + c], wv, sums[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < HP_TOKENS; ++t) sums[t] = warp_sum(sums[t]);
+        if (lane < count) {
+            float o = 0.0f;
+#pragma unroll
+            for (int t = 0; t < HP_TOKENS; ++t) if (t == lane) o = sums[t];
+            if (gate) {
+                const float g = to_float<T>(gate[(int64_t)(first + lane) * gate_token_stride + (int64_t)head * n + j]);
+                o = __fmul_rn(o, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g))));
+            }
+            out[(int64_t)(first + lane) * out_token_stride + head * out_head_stride + j] = from_float<T>(o);
+        }
+    }
+}
+
+// x [tokens, heads, k] and out [tokens, heads, n] with strides of their own; w contiguous [heads, n, k];
+// gate (optional) [tokens, heads * n] with a token stride.
+extern "C" int tvb_head_product(const void* x, long long x_token_stride, long long x_head_stride, const void* w,
+                                void* out, long long out_token_stride, long long out_head_stride, const void* gate,
+                                long long gate_token_stride, int tokens, int heads, int n, int k, int dtype,
+                                void* stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || n <= 0 || k <= 0) return TVB_BAD_ARGUMENT;
+    const size_t smem = (size_t)HP_TOKENS * k * sizeof(float);
+    if (smem > 48 * 1024) return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((tokens + HP_TOKENS - 1) / HP_TOKENS, heads);
+#define GO(T) head_product_kernel<T><<<grid, HP_WARPS * 32, smem, s>>>(                                          \
+        (const T*)x, x_token_stride, x_head_stride, (const T*)w, (T*)out, out_token_stride, out_head_stride,     \
+        (const T*)gate, gate_token_stride, tokens, n, k)
+    if (dtype == TVB_F32) GO(float);
+    else if (dtype == TVB_BF16) GO(bf16);
+    else return TVB_BAD_ARGUMENT;
+#undef GO
+    return tvb_last_error();
+}

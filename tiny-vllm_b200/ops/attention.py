@@ -282,16 +282,28 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
             raise kernels.KernelError("a layer blends its values with those of an earlier layer of the same "
                                       "shape, which has to run before it in the same step")
     position = mixer.position
+    if position is not None and getattr(position, "magnitude", 1.0) != 1.0:
+        raise kernels.KernelError("the kernel that prepares q and k here turns pairs without a factor on cosine "
+                                  "and sine; a scaled rotation needs the mixer that applies it")
+    head_norm = mixer.qk_norm
+    if head_norm == "whole":
+        # the norm over all heads at once (and the query temperature) first, in place; the preparing kernel
+        # then only stores k and v
+        kernels.projection_norm(
+            projected, [(q_at, mixer.q_cols, mixer.q_norm_weight, mixer.query_temperature is not None),
+                        (k_at, mixer.k_cols, mixer.k_norm_weight, False)],
+            ctx.positions, mixer.qk_norm_eps, temperature=mixer.query_temperature)
+        head_norm = None
     kernels.qkv_prepare(
         projected, q_at=q_at, k_at=k_at, v_at=v_at, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads,
-        key_dim=mixer.key_dim, value_dim=mixer.value_dim, positions=ctx.positions, norm=mixer.qk_norm,
+        key_dim=mixer.key_dim, value_dim=mixer.value_dim, positions=ctx.positions, norm=head_norm,
         q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps,
         inv_freq=None if position is None else position.inv_freq,
         rot_dims=0 if position is None else position.rot_dims,
         pairing="interleaved" if position is None else position.pairing,
         slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values,
         v_first=v_first, blend=mixer.vmix if v_first is not None else None)
-    gate = projected[:, g_at:g_at + mixer.out_cols] if mixer.gate else None
+    gate = projected[:, g_at:g_at + mixer.gate_cols] if mixer.gate else None
     queries = projected[:, q_at:q_at + mixer.q_cols]
     heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, key_dim=mixer.key_dim,
                  value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale)
@@ -325,13 +337,55 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
         queries, projected.stride(0), keys, values, ctx.block_tables[group],
         ctx.token_row, ctx.positions, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.key_dim,
         value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale,
-        gate=gate, out=out, scratch=scratch, max_chunks=ctx.split_chunks)
+        gate=gate, gate_per_head=mixer.gate == "head", slopes=mixer.slopes, sinks=mixer.sinks, out=out,
+        scratch=scratch, max_chunks=ctx.split_chunks)
+
+
+def latent_attention(ctx, mixer, projected: torch.Tensor, run: int) -> torch.Tensor:
+    """The attention of ``parts.LatentAttention`` between its input and output projections: from the
+    packed projection [tokens, q_rank | kv_rank + rot_dim | gate] to the gated, concatenated heads
+    [tokens, heads * value_dim]; writes the step's rows [latent | rotated key part] to the cache.
+
+    Every head attends the cached rows themselves: its query is [W_uk^T q_plain | q_rot] (the first part
+    a product a head, the second turned by the token's position), the values are the latents, and W_uv
+    turns the attended latent into the head's output, where the gate is applied.  Norms, angles, scores,
+    weights and sums are float32."""
+    keys, _ = ctx.storage.kv_of(run)
+    group = ctx.storage.group_of(run)
+    writes = ctx.writes_cache(run)
+    tokens = projected.shape[0]
+    heads, rank, rot = mixer.num_heads, mixer.kv_rank, mixer.rot_dim
+    position = mixer.position
+    inv_freq = None if position is None else position.inv_freq
+    magnitude = 1.0 if position is None else position.magnitude
+    q_latent = kernels.latent_prepare(
+        projected, dq_at=0, q_rank=mixer.q_rank, q_weight=mixer.dq_norm_weight, dkv_at=mixer.q_rank, kv_rank=rank,
+        kv_weight=mixer.dkv_norm_weight, rot_dim=rot, inv_freq=inv_freq, magnitude=magnitude,
+        positions=ctx.positions, slots=ctx.slots[group] if writes else None, key_cache=keys, eps=mixer.eps)
+    from .linear import linear
+
+    q = linear(q_latent, mixer.uq_weight).view(tokens, heads, mixer.key_dim + rot)
+    folded = torch.empty((tokens, heads, rank + rot), dtype=projected.dtype, device=projected.device)
+    kernels.head_product(q[:, :, :mixer.key_dim], mixer.uk_by_head, folded[:, :, :rank])
+    if rot > 0:
+        kernels.rotate_heads(q[:, :, mixer.key_dim:], folded[:, :, rank:], inv_freq, magnitude, ctx.positions)
+    scratch = None
+    if ctx.split_chunks > 0:
+        scratch = ctx.workspace(kernels.attention_rows_scratch_floats(tokens, heads, rank, ctx.split_chunks))
+    attended = kernels.attention_rows(
+        folded, folded.stride(0), keys, None, ctx.block_tables[group], ctx.token_row, ctx.positions,
+        num_q=heads, num_kv=1, head_dim=rank + rot, value_dim=rank, value_offset=0, window=None,
+        scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks)
+    gated = torch.empty((tokens, heads, mixer.value_dim), dtype=projected.dtype, device=projected.device)
+    gate = projected[:, mixer.q_rank + rank + rot:] if mixer.gate else None
+    kernels.head_product(attended.view(tokens, heads, rank), mixer.uv_by_head, gated, gate=gate)
+    return gated.view(tokens, heads * mixer.value_dim)
 
 
 def windowed_on_tensor_cores(mixer, projected: torch.Tensor, q_at: int, g_at: int, out: torch.Tensor) -> bool:
     """Whether the tensor-core kernels take this mixer's attention: bfloat16, key and value sizes
     that are multiples of 16, 16-byte aligned query rows; everything else goes to the row kernel."""
-    return (projected.dtype == torch.bfloat16 and TENSOR_CORE_WINDOWS
+    return (projected.dtype == torch.bfloat16 and TENSOR_CORE_WINDOWS and getattr(mixer, "plain", True)
             and kernels.attention_tiles_supports(mixer.key_dim, mixer.value_dim, mixer.num_heads, mixer.num_kv_heads)
             and projected.stride(0) % 8 == 0 and q_at % 8 == 0 and projected.data_ptr() % 16 == 0
             and g_at % 2 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)

@@ -286,6 +286,9 @@ def attention_chunk_keys() -> int:
     return _chunk_keys
 
 
+ATTENTION_ROWS_MAX_DIM = 640      # 32 lanes * ATTN_WIDE_DIMS of attention_rows.cu
+
+
 def attention_rows_scratch_floats(tokens: int, num_q: int, head_dim: int, max_chunks: int) -> int:
     """``head_dim``: the size of a value."""
     return tokens * num_q * max_chunks * (head_dim + 2)
@@ -297,7 +300,9 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
                    window: int | None, scale: float, out: torch.Tensor | None = None,
                    scratch: torch.Tensor | None = None, max_chunks: int = 0,
                    value_dim: int | None = None, keep_first: int = 0,
-                   gate: torch.Tensor | None = None) -> torch.Tensor:
+                   gate: torch.Tensor | None = None, gate_per_head: bool = False,
+                   slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                   value_offset: int | None = None) -> torch.Tensor:
     """Paged causal attention, one warp per (token, head).
 
     ``q`` holds the query heads of token t at ``t * q_token_stride`` elements
@@ -306,22 +311,38 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
     :func:`attention_rows_scratch_floats` long); 0 walks them in one warp.
     ``value_dim``: size of a value if it is not ``head_dim``; ``keep_first``: with a window, the
     first so many keys stay visible; ``gate`` [tokens, num_q * value_dim] (rows may be strided):
-    the output is multiplied by sigmoid(gate); ``out`` may have strided rows too."""
-    _need_cuda(q, key_cache, value_cache, block_tables, token_row, positions, scratch, gate)
+    the output is multiplied by sigmoid(gate); with ``gate_per_head`` the gate is [tokens, num_q],
+    one number a head; ``out`` may have strided rows too.  ``slopes`` (float32 [num_q]): slope *
+    (position - j) is taken off the score of key j; ``sinks`` (float32 [num_q]): exp(sink) joins the
+    softmax's denominator once.  ``value_offset``: the values are the ``value_dim`` elements from
+    there on of every key row (``value_cache`` is then None)."""
+    _need_cuda(q, key_cache, value_cache, block_tables, token_row, positions, scratch, gate, slopes, sinks)
     tokens = positions.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
-    if head_dim > 256 or value_dim > 256 or num_q % num_kv:
-        raise KernelError(f"attention_rows takes head sizes up to 256 and whole groups "
+    if head_dim > ATTENTION_ROWS_MAX_DIM or value_dim > ATTENTION_ROWS_MAX_DIM or num_q % num_kv:
+        raise KernelError(f"attention_rows takes head sizes up to {ATTENTION_ROWS_MAX_DIM} and whole groups "
                           f"(head_dim {head_dim}, {num_q} / {num_kv} heads)")
     if key_cache.dim() != 4 or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, head_dim) or \
-            value_cache.shape != key_cache.shape[:3] + (value_dim,) or key_cache.dtype != q.dtype or \
-            not key_cache.is_contiguous() or not value_cache.is_contiguous():
+            key_cache.dtype != q.dtype or not key_cache.is_contiguous():
         raise KernelError("attention_rows: caches must be contiguous [pages, num_kv, page_size, head_dim]")
-    for name, t in (("out", out), ("gate", gate)):
-        if t is not None and (t.dim() != 2 or t.shape != (tokens, num_q * value_dim) or t.stride(1) != 1
-                              or t.dtype != q.dtype):
-            raise KernelError(f"attention_rows: {name} must be [tokens, num_q * value_dim] of the dtype of q "
+    if value_offset is not None:
+        if value_cache is not None or not 0 <= value_offset <= head_dim - value_dim:
+            raise KernelError("attention_rows: values inside the key rows must fit them, and come without a "
+                              "value cache")
+        value_ptr, value_stride = key_cache.data_ptr() + value_offset * key_cache.element_size(), head_dim
+    else:
+        if value_cache.shape != key_cache.shape[:3] + (value_dim,) or not value_cache.is_contiguous() or \
+                value_cache.dtype != q.dtype:
+            raise KernelError("attention_rows: values must be contiguous [pages, num_kv, page_size, value_dim]")
+        value_ptr, value_stride = value_cache.data_ptr(), 0
+    gate_shape = (tokens, num_q) if gate_per_head else (tokens, num_q * value_dim)
+    for name, t, shape in (("out", out, (tokens, num_q * value_dim)), ("gate", gate, gate_shape)):
+        if t is not None and (t.dim() != 2 or t.shape != shape or t.stride(1) != 1 or t.dtype != q.dtype):
+            raise KernelError(f"attention_rows: {name} must be {list(shape)} of the dtype of q "
                               "with contiguous rows")
+    for name, t in (("slopes", slopes), ("sinks", sinks)):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (num_q,) or not t.is_contiguous()):
+            raise KernelError(f"attention_rows: {name} must be contiguous float32 [num_q]")
     for name, t in (("block_tables", block_tables), ("token_row", token_row), ("positions", positions)):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError(f"attention_rows: {name} must be contiguous int32")
@@ -333,14 +354,15 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
         need = attention_rows_scratch_floats(tokens, num_q, value_dim, max_chunks)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention_rows: split mode needs {need} float32 of scratch")
-    fn = _fn("attention_rows", "tvb_attention_rows_general",
-             [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-              c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-              c_int, c_int, c_float, c_int, c_void_p])
-    _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_cache.data_ptr(),
+    fn = _fn("attention_rows", "tvb_attention_rows_biased",
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_ptr, value_stride,
               block_tables.data_ptr(), block_tables.shape[1], token_row.data_ptr(),
               positions.data_ptr(), out.data_ptr(), out.stride(0), _ptr(gate),
-              0 if gate is None else gate.stride(0), _ptr(scratch), max_chunks, tokens, num_q, num_kv,
+              0 if gate is None else gate.stride(0), 1 if gate_per_head else 0, _ptr(slopes), _ptr(sinks),
+              _ptr(scratch), max_chunks, tokens, num_q, num_kv,
               head_dim, value_dim, key_cache.shape[2], window or 0, keep_first if window else 0, scale,
               dtype_tag(q.dtype), _stream()),
            "attention_rows", 2 if max_chunks > 0 else 1)
@@ -432,6 +454,208 @@ def sum_pair(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     _check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), dtype_tag(a.dtype), _stream()), "sum_pair")
     return out
 
+
+
+# ------------------------------------ layer norm behind the residual sum, over a float32 stream
+def post_layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, *, alpha: float = 1.0,
+                    add: torch.Tensor | None = None, rows: torch.Tensor | None = None,
+                    out_dtype: torch.dtype | None = None, want_stream: bool = True):
+    """out = LN(alpha * x + add) * weight, with mean, variance and the sum in float32.
+
+    ``x`` [tokens, width] is the residual stream (float32, or of the storage type where a model
+    starts it); ``add`` a sublayer's output (float32 or storage type) or None.  Returns (y, stream):
+    ``stream`` is ``out`` in float32 (a new tensor), ``y`` the same values rounded once to
+    ``out_dtype``; where ``out_dtype`` is float32 the two are one tensor.  With ``rows`` (int32) only
+    those rows are produced, and only y."""
+    _need_cuda(x, weight, add, rows)
+    if x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("post_layer_norm wants a contiguous [tokens, width] stream")
+    tokens, width = x.shape
+    if add is not None and (add.shape != x.shape or not add.is_contiguous()):
+        raise KernelError("post_layer_norm: the addend must match the stream")
+    if weight.shape != (width,) or width * 4 > 200 * 1024:
+        raise KernelError("post_layer_norm wants a weight [width] and a row that fits shared memory")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("post_layer_norm: rows must be int32")
+    out_dtype = out_dtype or (x.dtype if x.dtype != torch.float32 or weight.dtype == torch.float32 else weight.dtype)
+    count = tokens if rows is None else rows.shape[0]
+    want_stream = want_stream and rows is None
+    stream = torch.empty((count, width), dtype=torch.float32, device=x.device) \
+        if want_stream or out_dtype == torch.float32 else None
+    y = None if out_dtype == torch.float32 else torch.empty((count, width), dtype=out_dtype, device=x.device)
+    fn = _fn("post_norm", "tvb_post_layer_norm",
+             [c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_float, c_void_p])
+    _check(fn(x.data_ptr(), dtype_tag(x.dtype), alpha, _ptr(add), dtype_tag(add.dtype) if add is not None else F32,
+              weight.data_ptr(), dtype_tag(weight.dtype), _ptr(y), dtype_tag(out_dtype), _ptr(stream), _ptr(rows),
+              count, width, eps, _stream()), "post_layer_norm")
+    return (stream if y is None else y), stream
+
+
+def scale_float32(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x * factor in place, for a contiguous float32 tensor (logits that a model scales)."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_float32 wants a contiguous float32 tensor")
+    fn = _fn("post_norm", "tvb_scale_float32", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(fn(x.data_ptr(), x.numel(), factor, _stream()), "scale_float32")
+    return x
+
+
+# ------------------------------------------- norms over whole projections, latents, head products
+def projection_norm(proj: torch.Tensor, segments, positions: torch.Tensor | None, eps: float, *,
+                    temperature: tuple[float, int] | None = None) -> None:
+    """In place on a packed projection [tokens, columns]: every segment (first column, columns, weight
+    [columns], tempered) becomes v * rsqrt(mean(v^2) + eps) * weight over the whole segment; a tempered
+    segment is also multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) of the token's position p
+    (``temperature`` = (coef, every)).  One or two segments."""
+    _need_cuda(proj, positions, *[seg[2] for seg in segments])
+    if proj.dim() != 2 or proj.stride(1) != 1 or not 1 <= len(segments) <= 2:
+        raise KernelError("projection_norm wants [tokens, columns] with contiguous rows and one or two segments")
+    tokens = proj.shape[0]
+    for at, cols, weight, _ in segments:
+        if at < 0 or cols <= 0 or at + cols > proj.shape[1] or weight.shape != (cols,) or \
+                weight.dtype != segments[0][2].dtype or not weight.is_contiguous():
+            raise KernelError("projection_norm: a segment lies inside the row and has a weight of its size")
+    coef, every = temperature if temperature is not None else (0.0, 0)
+    if any(seg[3] for seg in segments) and every > 0 and (
+            positions is None or positions.dtype != torch.int32 or positions.shape != (tokens,)):
+        raise KernelError("projection_norm: a temperature needs int32 positions [tokens]")
+    first = segments[0]
+    second = segments[1] if len(segments) > 1 else (0, 0, None, False)
+    fn = _fn("latent_prepare", "tvb_projection_norm",
+             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+              c_float, c_float, c_int, c_int, c_int, c_void_p])
+    _check(fn(proj.data_ptr(), proj.stride(0), first[0], first[1], first[2].data_ptr(), int(bool(first[3])),
+              second[0], second[1], _ptr(second[2]), int(bool(second[3])), dtype_tag(first[2].dtype),
+              _ptr(positions), eps, float(coef), int(every), tokens, dtype_tag(proj.dtype), _stream()),
+           "projection_norm")
+
+
+def latent_prepare(proj: torch.Tensor, *, dq_at: int, q_rank: int, q_weight: torch.Tensor | None,
+                   dkv_at: int, kv_rank: int, kv_weight: torch.Tensor, rot_dim: int,
+                   inv_freq: torch.Tensor | None, magnitude: float, positions: torch.Tensor,
+                   slots: torch.Tensor | None, key_cache: torch.Tensor | None, eps: float) -> torch.Tensor | None:
+    """From a packed projection [tokens, columns] that holds a query latent (``q_rank`` columns from
+    ``dq_at``) and a key/value latent with a part to rotate (``kv_rank + rot_dim`` columns from
+    ``dkv_at``): returns RMSnorm(query latent) * q_weight [tokens, q_rank]; writes [RMSnorm(latent) *
+    kv_weight | rotated part] to ``key_cache`` [pages, 1, page, kv_rank + rot_dim] at ``slots``.  The
+    pair (2i, 2i + 1) turns by position * inv_freq[i] (float32), cosine and sine times ``magnitude``."""
+    _need_cuda(proj, q_weight, kv_weight, inv_freq, positions, slots, key_cache)
+    tokens = proj.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1 or min(dq_at, dkv_at) < 0 or \
+            max(dq_at + q_rank, dkv_at + kv_rank + rot_dim) > proj.shape[1]:
+        raise KernelError("latent_prepare: the latents do not fit the projection's rows")
+    if kv_weight.shape != (kv_rank,) or (q_rank > 0 and (q_weight is None or q_weight.shape != (q_rank,)
+                                                        or q_weight.dtype != kv_weight.dtype)):
+        raise KernelError("latent_prepare: norm weights of the latents' sizes and of one dtype")
+    if rot_dim % 2 or (rot_dim > 0 and (inv_freq is None or inv_freq.dtype != torch.float32
+                                        or inv_freq.shape != (rot_dim // 2,) or not inv_freq.is_contiguous())):
+        raise KernelError("latent_prepare: inv_freq must be float32 [rot_dim / 2]")
+    if positions.dtype != torch.int32 or positions.shape != (tokens,):
+        raise KernelError("latent_prepare: positions must be int32 [tokens]")
+    if slots is not None and (slots.dtype != torch.int32 or slots.shape != (tokens,) or key_cache is None
+                              or key_cache.dim() != 4 or key_cache.shape[1] != 1
+                              or key_cache.shape[3] != kv_rank + rot_dim or key_cache.dtype != proj.dtype
+                              or not key_cache.is_contiguous()):
+        raise KernelError("latent_prepare: slots int32 [tokens]; cache contiguous [pages, 1, page_size, "
+                          "kv_rank + rot_dim] of the projection's dtype")
+    q_latent = torch.empty((tokens, q_rank), dtype=proj.dtype, device=proj.device) if q_rank > 0 else None
+    fn = _fn("latent_prepare", "tvb_latent_prepare",
+             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
+              c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p])
+    _check(fn(proj.data_ptr(), proj.stride(0), dq_at, q_rank, _ptr(q_weight), _ptr(q_latent), q_rank, dkv_at,
+              kv_rank, kv_weight.data_ptr(), dtype_tag(kv_weight.dtype), rot_dim, _ptr(inv_freq), magnitude,
+              positions.data_ptr(), _ptr(slots), _ptr(key_cache) if slots is not None else None, eps, tokens,
+              dtype_tag(proj.dtype), _stream()), "latent_prepare")
+    return q_latent
+
+
+def _heads_view(t: torch.Tensor, heads: int, size: int, what: str) -> tuple[int, int]:
+    if t.dim() != 3 or t.shape[1:] != (heads, size) or t.stride(2) != 1:
+        raise KernelError(f"{what} must be [tokens, {heads}, {size}] with contiguous innermost elements")
+    return t.stride(0), t.stride(1)
+
+
+def rotate_heads(src: torch.Tensor, dst: torch.Tensor, inv_freq: torch.Tensor, magnitude: float,
+                 positions: torch.Tensor) -> None:
+    """dst[t, h, :] = src[t, h, :] with every pair (2i, 2i + 1) turned by position * inv_freq[i] and
+    cosine and sine multiplied by ``magnitude``; both [tokens, heads, rot_dim], any strides."""
+    _need_cuda(src, dst, inv_freq, positions)
+    tokens, heads, rot_dim = src.shape
+    s_strides = _heads_view(src, heads, rot_dim, "rotate_heads: src")
+    d_strides = _heads_view(dst, heads, rot_dim, "rotate_heads: dst")
+    if dst.shape != src.shape or dst.dtype != src.dtype or rot_dim % 2 or inv_freq.dtype != torch.float32 or \
+            inv_freq.shape != (rot_dim // 2,) or positions.dtype != torch.int32 or positions.shape != (tokens,):
+        raise KernelError("rotate_heads: equal shapes, float32 inv_freq [rot_dim / 2], int32 positions [tokens]")
+    fn = _fn("latent_prepare", "tvb_rotate_heads",
+             [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_int, c_int, c_void_p, c_float,
+              c_void_p, c_int, c_int, c_void_p])
+    _check(fn(src.data_ptr(), *s_strides, dst.data_ptr(), *d_strides, heads, rot_dim, inv_freq.data_ptr(),
+              magnitude, positions.data_ptr(), tokens, dtype_tag(src.dtype), _stream()), "rotate_heads")
+
+
+HEAD_PRODUCT_MAX_K = 1536        # eight float32 rows of x wait in 48 KB of shared memory
+
+
+def head_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, gate: torch.Tensor | None = None) -> None:
+    """out[t, h, j] = sum_k x[t, h, k] * w[h, j, k] for x [tokens, heads, k] and out [tokens, heads, n] with
+    strides of their own and contiguous w [heads, n, k]; with ``gate`` [tokens, heads * n] the result is
+    multiplied by sigmoid(gate) before it is rounded.  float32 sums in an order that k alone fixes."""
+    _need_cuda(x, w, out, gate)
+    if w.dim() != 3 or not w.is_contiguous():
+        raise KernelError("head_product wants contiguous weights [heads, n, k]")
+    heads, n, k = w.shape
+    tokens = x.shape[0]
+    x_strides = _heads_view(x, heads, k, "head_product: x")
+    o_strides = _heads_view(out, heads, n, "head_product: out")
+    if out.shape[0] != tokens or not (x.dtype == w.dtype == out.dtype) or k > HEAD_PRODUCT_MAX_K:
+        raise KernelError(f"head_product: one dtype, equal token counts, k up to {HEAD_PRODUCT_MAX_K}")
+    if gate is not None and (gate.shape != (tokens, heads * n) or gate.stride(1) != 1 or gate.dtype != x.dtype):
+        raise KernelError("head_product: gate must be [tokens, heads * n] of the same dtype with contiguous rows")
+    fn = _fn("latent_prepare", "tvb_head_product",
+             [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong,
+              c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(x.data_ptr(), *x_strides, w.data_ptr(), out.data_ptr(), *o_strides, _ptr(gate),
+              0 if gate is None else gate.stride(0), tokens, heads, n, k, dtype_tag(x.dtype), _stream()),
+           "head_product")
+
+
+# ----------------------------------------------------------- routing of a mixture of experts
+EXPERT_ACTIVATIONS = {"relu_squared": 0, "silu": 1}
+ROUTE_MAX_EXPERTS = 1024
+
+
+def route_act(logits: torch.Tensor, up: torch.Tensor, *, experts: int, top: int, ff: int, shared_ff: int,
+              activation: str = "relu_squared", out: torch.Tensor | None = None,
+              weights_out: torch.Tensor | None = None) -> torch.Tensor:
+    """From router logits (float32 [tokens, experts]) and the packed up-projection [tokens, experts * ff
+    + shared_ff] to the input of the packed down-projection: act(up) times the expert's weight (the softmax
+    over the ``top`` largest logits; 0 for every other expert), the shared expert's columns unweighted."""
+    _need_cuda(logits, up, out, weights_out)
+    tokens = up.shape[0]
+    columns = experts * ff + shared_ff
+    if activation not in EXPERT_ACTIVATIONS:
+        raise KernelError(f"route_act knows {', '.join(EXPERT_ACTIVATIONS)}, not {activation!r}")
+    if logits.dtype != torch.float32 or logits.shape != (tokens, experts) or logits.stride(1) != 1:
+        raise KernelError("route_act: router logits are float32 [tokens, experts]")
+    if up.dim() != 2 or up.shape[1] != columns or up.stride(1) != 1 or not 0 < experts <= ROUTE_MAX_EXPERTS \
+            or top <= 0:
+        raise KernelError("route_act: up must be [tokens, experts * ff + shared_ff] with contiguous rows")
+    if out is None:
+        out = torch.empty((tokens, columns), dtype=up.dtype, device=up.device)
+    elif out.shape != (tokens, columns) or out.dtype != up.dtype or out.stride(1) != 1:
+        raise KernelError("route_act: out must match up")
+    if weights_out is not None and (weights_out.dtype != torch.float32 or weights_out.shape != (tokens, experts)
+                                    or not weights_out.is_contiguous()):
+        raise KernelError("route_act: weights_out must be contiguous float32 [tokens, experts]")
+    fn = _fn("routed_act", "tvb_route_act",
+             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(logits.data_ptr(), logits.stride(0), up.data_ptr(), up.stride(0), out.data_ptr(), out.stride(0),
+              _ptr(weights_out), tokens, experts, top, ff, shared_ff, EXPERT_ACTIVATIONS[activation],
+              dtype_tag(up.dtype), _stream()), "route_act")
+    return out
 
 # ------------------- q/k norm, rotation, value blend and cache write with every size a parameter
 NORM_MODES = {None: 0, "unit": 1, "weight": 2}

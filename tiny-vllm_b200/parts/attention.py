@@ -105,6 +105,15 @@ class WindowedAttention(Part):
     values on to the later layers of the step under ``value_mix_key``; "blend" replaces v by
     (1 - l) v + l v_first, with the scalar tensor ``vmix`` as l, before it is cached.
 
+    ``qk_norm="whole"``: q and k are divided by their root mean square over the whole projection,
+    all heads at once, and multiplied by weights of that size (``q_norm`` / ``k_norm``).
+    ``query_temperature`` (coef, every): q at position p is multiplied by 1 + coef * ln(floor((p + 1) /
+    every) + 1).  ``distance_slope_exponent`` = c: head h takes 2^(-c (h + 1) / heads) * (i - j) off
+    the score of key j for query i.  ``sink``: a learned number a head (tensor ``sink``) whose
+    exponential joins the softmax's denominator once, with no key and no value.  ``gate="head"``:
+    the gate is one number a head, sigmoid(W_g x)_h with W_g [heads, width].  ``float32_output``: the
+    output projection leaves its float32 sums unrounded (for a float32 residual sum).
+
     ``hosted=True``: a block computes the input projections of all its parts as one product and
     the output projections as another; the mixer then owns no matrices, names its share
     (``input_rows``, ``output_cols``) and works between the two products (``between``)."""
@@ -112,14 +121,20 @@ class WindowedAttention(Part):
     def __init__(self, ctx: BuildContext, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  key_dim: int, value_dim: int, scale: float, window: int | None = None,
                  keep_first: int = 0, qk_norm: str | None = None, qk_norm_eps: float = 0.0,
-                 position=None, gate: bool = False, value_mix: str | None = None,
-                 value_mix_key: str = "v_first", names: dict | None = None, hosted: bool = False) -> None:
+                 position=None, gate: bool | str = False, value_mix: str | None = None,
+                 value_mix_key: str = "v_first", names: dict | None = None, hosted: bool = False,
+                 query_temperature: tuple | None = None, distance_slope_exponent: float | None = None,
+                 sink: bool = False, float32_output: bool = False) -> None:
         if num_heads % num_kv_heads:
             raise ValueError("query heads must be a multiple of key-value heads")
         if not 0 < key_dim <= 256 or not 0 < value_dim <= 256:
             raise ValueError(f"the attention kernels take key and value sizes up to 256, not {key_dim} / {value_dim}")
-        if qk_norm not in (None, "unit", "weight"):
-            raise ValueError(f"qk_norm is None, 'unit' or 'weight', not {qk_norm!r}")
+        if qk_norm not in (None, "unit", "weight", "whole"):
+            raise ValueError(f"qk_norm is None, 'unit', 'weight' or 'whole', not {qk_norm!r}")
+        if gate not in (False, True, "head"):
+            raise ValueError(f"gate is False, True or 'head', not {gate!r}")
+        if query_temperature is not None and qk_norm != "whole":
+            raise ValueError("the query temperature is applied by the norm over the whole projection")
         if value_mix not in (None, "first", "blend"):
             raise ValueError(f"value_mix is None, 'first' or 'blend', not {value_mix!r}")
         if window is not None and window <= 0:
@@ -136,8 +151,17 @@ class WindowedAttention(Part):
         self.gate = gate
         self.value_mix, self.value_mix_key = value_mix, value_mix_key
         self.hosted = hosted
+        self.query_temperature = None if query_temperature is None else (float(query_temperature[0]),
+                                                                          int(query_temperature[1]))
+        if self.query_temperature is not None and self.query_temperature[1] <= 0:
+            raise ValueError("the query temperature's period must be positive")
+        self.distance_slope_exponent = None if distance_slope_exponent is None else float(distance_slope_exponent)
+        self.has_sink = bool(sink)
+        self.out_dtype = torch.float32 if float32_output else None
+        self.device = ctx.device
+        self.slopes = self.sinks = self.sink = None
         n = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "vmix": "vmix", "q_norm": "q_norm",
-             "k_norm": "k_norm", **(names or {})}
+             "k_norm": "k_norm", "sink": "sink", **(names or {})}
         self.names = {key: f"{ctx.prefix}.{value}" for key, value in n.items()}
         self.position = ctx.build("position", position, ctx) if position is not None else None
         self.in_weight = self.o_weight = self.vmix = self.q_norm_weight = self.k_norm_weight = None
@@ -159,12 +183,22 @@ class WindowedAttention(Part):
     def out_cols(self) -> int:
         return self.num_heads * self.value_dim
 
+    @property
+    def gate_cols(self) -> int:
+        return 0 if not self.gate else self.num_heads if self.gate == "head" else self.out_cols
+
+    @property
+    def plain(self) -> bool:
+        """No distance bias, no sink, a gate (if any) of one number a value, keys and values apart:
+        what the tensor-core kernels of the windowed attention take."""
+        return self.distance_slope_exponent is None and not self.has_sink and self.gate != "head"
+
     def input_rows(self):
         """(checkpoint tensor, rows) of the input projections, in the order of their columns:
         q heads, k heads, v heads and, with a gate, the gate."""
         rows = [(self.names["q"], self.q_cols), (self.names["k"], self.k_cols), (self.names["v"], self.v_cols)]
         if self.gate:
-            rows.append((self.names["g"], self.out_cols))
+            rows.append((self.names["g"], self.gate_cols))
         return rows
 
     def output_cols(self):
@@ -183,7 +217,23 @@ class WindowedAttention(Part):
                                        role="vector", init="around_one"),
                       ParamSpec.single("k_norm_weight", self.names["k_norm"], (self.key_dim,),
                                        role="vector", init="around_one")]
+        if self.qk_norm == "whole":
+            specs += [ParamSpec.single("q_norm_weight", self.names["q_norm"], (self.q_cols,),
+                                       role="vector", init="around_one"),
+                      ParamSpec.single("k_norm_weight", self.names["k_norm"], (self.k_cols,),
+                                       role="vector", init="around_one")]
+        if self.has_sink:
+            specs.append(ParamSpec.single("sink", self.names["sink"], (self.num_heads,), role="vector"))
         return specs
+
+    def finalize(self) -> None:
+        """The per-head constants of the attention kernels, float32 on the device."""
+        if self.distance_slope_exponent is not None:
+            heads = torch.arange(1, self.num_heads + 1, dtype=torch.float64)
+            self.slopes = (2.0 ** (-self.distance_slope_exponent * heads / self.num_heads)).to(
+                torch.float32).to(self.device)
+        if self.has_sink and self.sink is not None:
+            self.sinks = self.sink.to(torch.float32).contiguous()
 
     def children(self):
         return [self.position] if self.position is not None else []
@@ -215,8 +265,103 @@ class WindowedAttention(Part):
         projected = linear(x, self.in_weight)
         attended = torch.empty((x.shape[0], self.out_cols), dtype=x.dtype, device=x.device)
         self.between(projected, 0, ctx, attended, run)
-        return linear(attended, self.o_weight)
+        return linear(attended, self.o_weight, out_dtype=self.out_dtype)
+
+
+class LatentAttention(Part):
+    """Attention whose queries, keys and values come through low-rank latents.
+
+    c_q = RMSnorm(W_dq x) (weight ``dq.norm``), q = W_uq c_q, a head being [``key_dim`` plain |
+    ``rot_dim`` rotated] dimensions.  W_dkv x has ``kv_rank + rot_dim`` rows: the first, RMS-normed
+    (weight ``dkv.norm``), are the latent c, the rest one rotated key part that all heads share.  A
+    head's plain key is W_uk c and its value W_uv c; the score is (q_plain . k_plain + q_rot . k_rot) *
+    scale, softmax over the causal keys.  The concatenated heads are multiplied by sigmoid(W_g x)
+    (``gate``) and projected by W_o.
+
+    Only [c | rotated key part] is cached, as one key row a token of one kv head.  The up-projections
+    never touch the cache: W_uk is folded into the query (q_plain^T W_uk is a query over c itself,
+    so every head attends rows [c | k_rot] with the query [W_uk^T q_plain | q_rot]), the attention's
+    values are the first ``kv_rank`` elements of the same rows, and W_uv is applied to the attended
+    latent afterwards, a head at a time."""
+
+    def __init__(self, ctx: BuildContext, *, hidden_size: int, num_heads: int, key_dim: int, rot_dim: int,
+                 value_dim: int, q_rank: int, kv_rank: int, scale: float, eps: float, position=None,
+                 gate: bool = True, float32_output: bool = False, names: dict | None = None) -> None:
+        if rot_dim % 2:
+            raise ValueError("the rotated part of a head has an even size")
+        if (rot_dim > 0) != (position is not None):
+            raise ValueError("a rotated part needs a position part, and only then")
+        if kv_rank + rot_dim > kernels.ATTENTION_ROWS_MAX_DIM:
+            raise ValueError(f"latent and rotated part together may hold up to {kernels.ATTENTION_ROWS_MAX_DIM} "
+                             f"elements, not {kv_rank + rot_dim}")
+        self.hidden_size, self.num_heads = hidden_size, num_heads
+        self.key_dim, self.rot_dim, self.value_dim = key_dim, rot_dim, value_dim
+        self.q_rank, self.kv_rank = q_rank, kv_rank
+        self.scale, self.eps = float(scale), float(eps)
+        self.gate = bool(gate)
+        self.out_dtype = torch.float32 if float32_output else None
+        n = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
+             "uv": "uv", "g": "g", "o": "o", **(names or {})}
+        self.names = {key: f"{ctx.prefix}.{value}" for key, value in n.items()}
+        self.position = ctx.build("position", position, ctx) if position is not None else None
+        if self.position is not None and (getattr(self.position, "pairing", None) != "interleaved"
+                                          or self.position.rot_dims != rot_dim):
+            raise ValueError("the rotated part is turned as neighbouring pairs over its whole size")
+        self.in_weight = self.uq_weight = self.uk_weight = self.uv_weight = self.o_weight = None
+        self.dq_norm_weight = self.dkv_norm_weight = None
+        self.uk_by_head = self.uv_by_head = None
+
+    @property
+    def out_cols(self) -> int:
+        return self.num_heads * self.value_dim
+
+    @property
+    def row_dim(self) -> int:
+        """Size of a cached row: the latent and the rotated key part."""
+        return self.kv_rank + self.rot_dim
+
+    def param_specs(self):
+        rows = [(self.names["dq"], self.q_rank), (self.names["dkv"], self.row_dim)]
+        if self.gate:
+            rows.append((self.names["g"], self.out_cols))
+        return [
+            ParamSpec.packed("in_weight", rows, self.hidden_size),
+            ParamSpec.single("dq_norm_weight", self.names["dq_norm"], (self.q_rank,), role="vector", init="around_one"),
+            ParamSpec.single("dkv_norm_weight", self.names["dkv_norm"], (self.kv_rank,), role="vector",
+                             init="around_one"),
+            ParamSpec.single("uq_weight", self.names["uq"], (self.num_heads * (self.key_dim + self.rot_dim), self.q_rank)),
+            ParamSpec.single("uk_weight", self.names["uk"], (self.num_heads * self.key_dim, self.kv_rank)),
+            ParamSpec.single("uv_weight", self.names["uv"], (self.out_cols, self.kv_rank)),
+            ParamSpec.single("o_weight", self.names["o"], (self.hidden_size, self.out_cols)),
+        ]
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def finalize(self) -> None:
+        """The up-projections a head at a time, as the head products read them: W_uk transposed
+        ([heads, kv_rank, key_dim]: the product with it folds W_uk into the query), W_uv as it is."""
+        self.uk_by_head = self.uk_weight.view(self.num_heads, self.key_dim, self.kv_rank).transpose(1, 2).contiguous()
+        self.uv_by_head = self.uv_weight.view(self.num_heads, self.value_dim, self.kv_rank)
+
+    def streamed_weights(self):
+        return [self.in_weight, self.uq_weight, self.o_weight]
+
+    def cache_need(self):
+        return KVNeed(1, self.row_dim, None, self.kv_rank, 0, value_offset=0)
+
+    def takes_tensor_memory_tiles(self, page_size: int) -> bool:
+        return False
+
+    def scratch_floats(self, rows: int, chunks: int) -> int:
+        return kernels.attention_rows_scratch_floats(rows, self.num_heads, self.kv_rank, chunks)
+
+    def forward(self, x, ctx, run: int):
+        projected = linear(x, self.in_weight)
+        gated = attention_ops.latent_attention(ctx, self, projected, run)
+        return linear(gated, self.o_weight, out_dtype=self.out_dtype)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)
+register_part("mixer", "latent_attention", LatentAttention)
 register_part("mixer", "windowed_attention", WindowedAttention)

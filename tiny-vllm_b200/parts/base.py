@@ -114,13 +114,16 @@ class ParamSpec:
 class KVNeed:
     """A growing cache of keys and values, ``window`` keys long if given.  ``value_dim``: the size
     of a value where it differs from that of a key (``head_dim``).  ``keep_first``: a windowed
-    cache never lets go of its first so many tokens (queries keep seeing them)."""
+    cache never lets go of its first so many tokens (queries keep seeing them).  ``value_offset``:
+    the value is not stored apart but is the ``value_dim`` elements from there on of the key's row
+    (attention over a latent that serves as key and value at once): the cache holds no value pages."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
     keep_first: int = 0
+    value_offset: int | None = None
 
     @property
     def value_size(self) -> int:
@@ -129,7 +132,7 @@ class KVNeed:
     def geometry(self) -> tuple:
         """What two runs must agree on to share pages and block tables."""
         return (self.num_kv_heads, self.head_dim, self.value_size, self.window,
-                self.keep_first if self.window is not None else 0)
+                self.keep_first if self.window is not None else 0, self.value_offset)
 
 
 @dataclass(frozen=True)

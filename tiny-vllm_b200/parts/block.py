@@ -115,5 +115,50 @@ class ParallelResidualBlock(Block):
         return linear(inner, self.out_weight, out_dtype=torch.float32), residual
 
 
+class PostNormResidualBlock(Block):
+    """Norm after the sum: x <- norm1(alpha * x + mixer(x)), then x <- norm2(alpha * x +
+    feed_forward(x)); both sublayers read x itself.  A layer may have no feed-forward (and then no
+    second norm).  The stream x is float32 whatever the storage type; the norms hand on, beside it,
+    its one rounding to the storage type (``stream.rounded``), which is what the next products read.
+    The block returns (None, stream): nothing is left to add."""
+
+    def __init__(self, ctx: BuildContext, *, mixer, feed_forward, norm, alpha: float, mixer_norm_name: str,
+                 feed_forward_norm_name: str, mixer_name: str, feed_forward_name: str) -> None:
+        self.alpha = float(alpha)
+        # the norms' weights are stored under the norms' own names, "<layer>.<norm name>"
+        self.mixer_norm = ctx.build("norm", norm.with_params(name=f"{ctx.prefix}.{mixer_norm_name}"), ctx)
+        self.mixer = ctx.build("mixer", mixer, ctx.child(mixer_name))
+        self.feed_forward = self.feed_forward_norm = None
+        if feed_forward is not None:
+            self.feed_forward_norm = ctx.build(
+                "norm", norm.with_params(name=f"{ctx.prefix}.{feed_forward_norm_name}"), ctx)
+            self.feed_forward = ctx.build("feed_forward", feed_forward, ctx.child(feed_forward_name))
+        for part in (self.mixer_norm, self.feed_forward_norm):
+            if part is not None and not hasattr(part, "post"):
+                raise ValueError("a post-norm block needs norms that offer post(x, y, alpha)")
+
+    def children(self):
+        return [part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+                if part is not None]
+
+    def forward(self, hidden, residual, ctx, run: int):
+        if residual is None:                 # the first block: the embedding starts the stream
+            stream, x = hidden, hidden
+        else:
+            if hidden is not None:
+                raise ValueError("a post-norm block follows blocks that leave nothing to add to the stream")
+            stream = residual
+            x = getattr(stream, "rounded", None)
+            if x is None:
+                x = stream if stream.dtype == self.mixer_norm.out_dtype else stream.to(self.mixer_norm.out_dtype)
+        x, stream = self.mixer_norm.post(stream, self.mixer.forward(x, ctx, run), self.alpha)
+        if self.feed_forward is not None:
+            x, stream = self.feed_forward_norm.post(stream, self.feed_forward.forward(x, ctx), self.alpha)
+        if x is not stream:
+            stream.rounded = x
+        return None, stream
+
+
 register_part("block", "prenorm_residual", PreNormResidualBlock)
+register_part("block", "postnorm_residual", PostNormResidualBlock)
 register_part("block", "parallel_residual", ParallelResidualBlock)

@@ -27,8 +27,9 @@ class TokenEmbedding(Part):
 
 class LMHead(Part):
     def __init__(self, ctx: BuildContext, *, vocab_size: int, width: int, name: str,
-                 tied_to: str | None) -> None:
+                 tied_to: str | None, scale: float = 1.0) -> None:
         self.vocab_size, self.width, self.name, self.tied_to = vocab_size, width, name, tied_to
+        self.scale = float(scale)          # the float32 logits are multiplied by it
         self.weight = None
 
     def param_specs(self):
@@ -40,7 +41,8 @@ class LMHead(Part):
         return [self.weight]
 
     def forward(self, hidden_rows):
-        return linear(hidden_rows, self.weight, out_dtype=torch.float32)
+        logits = linear(hidden_rows, self.weight, out_dtype=torch.float32)
+        return logits if self.scale == 1.0 else kernels.scale_float32(logits, self.scale)
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -13,6 +13,8 @@ its columns of the common input of the output product (``between``).
 
 from __future__ import annotations
 
+import torch
+
 from ..ops import kernels, linear, linear_into_stream, linear_norm, linear_silu
 from .base import BuildContext, ParamSpec, Part
 from .registry import register_part
@@ -87,3 +89,56 @@ class SwiGLU(Part):
 
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "gated_mlp", SwiGLU)
+
+
+class RoutedExperts(Part):
+    """A mixture of small feed-forward experts, down_e(act(up_e h)), without biases.
+
+    Router logits z = W_router h are float32; each token uses the ``top`` experts with the largest
+    logits, weighted by the softmax over those logits alone; a shared expert of the same form (size
+    ``shared_ff``, 0 for none) runs for every token and is added.
+
+    The experts' up-projections are the rows of one weight [experts * ff + shared_ff, width] and their
+    down-projections stand side by side in one weight [width, experts * ff + shared_ff]: between the
+    two products one kernel picks the experts, turns their logits into weights and stores act(up) *
+    weight (0 for experts that were not chosen), so that the second product is the weighted sum of
+    the chosen experts' outputs plus the shared expert's, accumulated in float32.  Every token pays
+    for all experts' columns: the form for few, small experts."""
+
+    def __init__(self, ctx: BuildContext, *, hidden_size: int, experts: int, top: int, ff: int,
+                 shared_ff: int = 0, activation: str = "relu_squared", float32_output: bool = False,
+                 names: dict | None = None) -> None:
+        if activation not in kernels.EXPERT_ACTIVATIONS:
+            raise ValueError(f"activation is one of {', '.join(kernels.EXPERT_ACTIVATIONS)}, not {activation!r}")
+        if not 0 < top <= experts or experts > kernels.ROUTE_MAX_EXPERTS:
+            raise ValueError(f"a token uses between 1 and all of at most {kernels.ROUTE_MAX_EXPERTS} experts")
+        self.hidden_size, self.experts, self.top, self.ff, self.shared_ff = hidden_size, experts, top, ff, shared_ff
+        self.activation = activation
+        self.out_dtype = torch.float32 if float32_output else None
+        n = {"router": "router", "expert": "e{index}", "shared": "shared", "up": "up", "down": "down",
+             **(names or {})}
+        self.router_name = f"{ctx.prefix}.{n['router']}"
+        stems = [f"{ctx.prefix}.{n['expert'].format(index=index)}" for index in range(experts)]
+        if shared_ff:
+            stems.append(f"{ctx.prefix}.{n['shared']}")
+        sizes = [ff] * experts + ([shared_ff] if shared_ff else [])
+        self.up_sources = [(f"{stem}.{n['up']}", size) for stem, size in zip(stems, sizes)]
+        self.down_sources = [(f"{stem}.{n['down']}", size) for stem, size in zip(stems, sizes)]
+        self.router_weight = self.up_weight = self.down_weight = None
+
+    def param_specs(self):
+        return [ParamSpec.single("router_weight", self.router_name, (self.experts, self.hidden_size)),
+                ParamSpec.packed("up_weight", self.up_sources, self.hidden_size),
+                ParamSpec.side_by_side("down_weight", self.hidden_size, self.down_sources)]
+
+    def streamed_weights(self):
+        return [self.up_weight, self.down_weight]
+
+    def forward(self, x, ctx):
+        logits = linear(x, self.router_weight, out_dtype=torch.float32)
+        inner = kernels.route_act(logits, linear(x, self.up_weight), experts=self.experts, top=self.top,
+                                  ff=self.ff, shared_ff=self.shared_ff, activation=self.activation)
+        return linear(inner, self.down_weight, out_dtype=self.out_dtype)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -77,5 +77,43 @@ class StreamRMSNorm(Part):
                                    out_dtype=self.out_dtype)[0]
 
 
+class StreamLayerNorm(Part):
+    """Layer norm with a weight and no bias over a float32 residual stream, for blocks that norm after
+    the sum: out = (s - mean(s)) / sqrt(mean((s - mean)^2) + eps) * weight with s = alpha * x + y, all
+    in float32.  ``post`` returns (out rounded once to the storage type, out in float32): the first
+    feeds the next products, the second is the stream.  In the float32 path both are one tensor."""
+
+    def __init__(self, ctx: BuildContext, *, width: int, eps: float, name: str | None = None) -> None:
+        self.width = width
+        self.eps = float(eps)
+        self.name = name if name is not None else f"{ctx.prefix}.weight"
+        self.out_dtype = ctx.dtype
+        self.weight = None
+
+    def param_specs(self):
+        return [ParamSpec.single("weight", self.name, (self.width,), role="vector", init="around_one")]
+
+    def post(self, x, y, alpha: float = 1.0):
+        """(LN(alpha * x + y) in the storage type, the same in float32); y may be None."""
+        return kernels.post_layer_norm(x, self.weight, self.eps, alpha=alpha, add=y, out_dtype=self.out_dtype)
+
+    def forward(self, x):
+        return self.post(x, None)[0]
+
+    def add(self, x, residual):
+        """(LN(residual + x), the same in float32)."""
+        if residual is None:
+            return self.post(x, None)
+        return self.post(residual, x)
+
+    def add_rows(self, x, residual, rows):
+        """LN(residual + x) on the rows named by ``rows`` only (x alone without a residual)."""
+        if residual is None:
+            x, residual = None, x
+        return kernels.post_layer_norm(residual, self.weight, self.eps, add=x, rows=rows,
+                                       out_dtype=self.out_dtype)[0]
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "layer_norm_stream32", StreamLayerNorm)
 register_part("norm", "rms_norm_stream32", StreamRMSNorm)

@@ -9,6 +9,8 @@ gathers and casts them per step, tinyvllm/layers.py:229-245).
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..ops import kernels
@@ -51,22 +53,49 @@ class RopeInterleaved(Part):
     """Rotary encoding with neighbouring dimensions paired: (2i, 2i + 1) of the first ``dims``
     dimensions of a head turn by position * base^(-2i / dims); the rest of the head passes.  No
     tables: the kernel that prepares q and k multiplies the position with ``inv_freq`` (float32)
-    and takes sine and cosine itself, so there is no limit on positions."""
+    and takes sine and cosine itself, so there is no limit on positions.
+
+    ``scaling`` (``factor``, ``original``, ``fast``, ``slow``) stretches the slow pairs for contexts
+    beyond ``original`` positions: with d(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo =
+    max(floor(d(fast)), 0), hi = min(ceil(d(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo,
+    0.001), 0, 1), pair i turns at f_i / factor * ramp_i + f_i * (1 - ramp_i), and cosine and sine are
+    multiplied by ``magnitude`` = 0.1 ln(factor) + 1 (1 without scaling)."""
 
     pairing = "interleaved"
 
-    def __init__(self, ctx: BuildContext, *, dims: int, base: float) -> None:
+    def __init__(self, ctx: BuildContext, *, dims: int, base: float, scaling: dict | None = None) -> None:
         if dims <= 0 or dims % 2:
             raise ValueError("rotary encoding needs an even, positive number of dimensions")
         self.rot_dims = dims
         self.base = float(base)
+        self.scaling = dict(scaling) if scaling else None
+        self.magnitude = 1.0
+        if self.scaling is not None:
+            missing = [key for key in ("factor", "original", "fast", "slow") if key not in self.scaling]
+            if missing:
+                raise ValueError("rotary scaling lacks " + ", ".join(missing))
+            if not self.scaling["factor"] > 0:
+                raise ValueError("the scaling factor must be positive")
+            self.magnitude = 0.1 * math.log(float(self.scaling["factor"])) + 1.0
         self.device = ctx.device
         self.inv_freq = None
 
     def inverse_frequencies(self) -> torch.Tensor:
-        """base^(-2i / dims), evaluated in double precision and rounded to float32 once."""
+        """The pairs' frequencies, evaluated in double precision and rounded to float32 once."""
         exponent = torch.arange(0, self.rot_dims, 2, dtype=torch.float64) / self.rot_dims
-        return (self.base ** -exponent).to(torch.float32)
+        freqs = self.base ** -exponent
+        if self.scaling is not None:
+            factor, original = float(self.scaling["factor"]), float(self.scaling["original"])
+
+            def dimension(turns: float) -> float:
+                return self.rot_dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+            lo = max(math.floor(dimension(float(self.scaling["fast"]))), 0)
+            hi = min(math.ceil(dimension(float(self.scaling["slow"]))), self.rot_dims - 1)
+            index = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+            ramp = ((index - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            freqs = freqs / factor * ramp + freqs * (1.0 - ramp)
+        return freqs.to(torch.float32)
 
     def finalize(self) -> None:
         self.inv_freq = self.inverse_frequencies().to(self.device)
