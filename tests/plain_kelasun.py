@@ -111,7 +111,7 @@ def latent_attention(h, w, prefix, mixer, eps):
                                        mixer["kv_rank"])
     n = h.shape[0]
     positions = list(range(n))
-    freqs, magnitude = rotary_frequencies(mixer["rot"])
+    freqs, magnitude = rotary_frequencies(mixer["rot"]) if rot_dim else ([], 1.0)
     c_q = rms_norm(h @ w[f"{prefix}.dq"].T, w[f"{prefix}.dq.norm"], eps)
     q = (c_q @ w[f"{prefix}.uq"].T).view(n, heads, dim + rot_dim)
     down = h @ w[f"{prefix}.dkv"].T
