@@ -200,15 +200,17 @@ def _paged(keys, values, page, dtype, seed, fill=float("nan")):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("split", [False, True], ids=["rows", "split"])
-@pytest.mark.parametrize("heads,kv,dk,dv", [(4, 2, 16, 32), (3, 1, 9, 20), (8, 8, 32, 16)])
-def test_attention_with_distance_bias_sink_and_head_gate(heads, kv, dk, dv, split, dtype):
+@pytest.mark.parametrize("kind", ["rows", "split", "tiles", "singles"])
+@pytest.mark.parametrize("heads,kv,dk,dv", [(4, 2, 16, 32), (3, 1, 9, 20), (8, 8, 32, 16), (40, 2, 16, 16)])
+def test_attention_with_distance_bias_sink_and_head_gate(heads, kv, dk, dv, kind, dtype):
     """Random scores plus one key per checked query that is made to stand out: far back (position 3 from
     position 700), at both sides of a page border and of a chunk border of 256 keys, the query's own.
     The distance bias takes slope * distance off it, the sink shares the denominator, the gate is one
     number a head."""
     from tinyvllm_b200.ops import kernels
 
+    if kind in ("tiles", "singles") and (dtype != torch.bfloat16 or dk % 16 or dv % 16):
+        pytest.skip("the tensor-core kernels take bfloat16 and sizes in steps of 16")
     n, page, scale = 701, 8, 0.4
     g = torch.Generator().manual_seed(heads * 100 + dk)
     q = torch.randn(n, heads, dk, generator=g)
@@ -238,27 +240,54 @@ def test_attention_with_distance_bias_sink_and_head_gate(heads, kv, dk, dv, spli
         scores = (q[:, h] @ k[:, group].T) * scale - slopes[h] * distance
         weights = plain.causal_softmax_rows(scores, sink=sinks[h])
         want[:, h] = (weights @ v[:, group])[rows] * torch.sigmoid(gate[rows, h:h + 1])
-    key_cache, value_cache, table = _paged(k, v, page, dtype, 3)
-    positions = torch.tensor(rows, dtype=torch.int32, device=CUDA)
-    chunks = 3 if split else 0
-    scratch = torch.empty(kernels.attention_rows_scratch_floats(len(rows), heads, dv, 3), dtype=torch.float32,
-                          device=CUDA) if split else None
-    got = kernels.attention_rows(
-        q[rows].to(dtype).reshape(len(rows), heads * dk).to(CUDA), heads * dk, key_cache.to(CUDA), value_cache.to(CUDA),
-        table.to(CUDA), torch.zeros(len(rows), dtype=torch.int32, device=CUDA), positions, num_q=heads, num_kv=kv,
-        head_dim=dk, value_dim=dv, window=None, scale=scale, gate=gate[rows].to(dtype).to(CUDA), gate_per_head=True,
-        slopes=slopes.float().to(CUDA), sinks=sinks.float().to(CUDA), scratch=scratch, max_chunks=chunks)
+    key_cache, value_cache, table = _paged(k, v, page, dtype, 3, fill=float("nan") if kind in ("rows", "split") else 1e30)
+    extras = dict(gate_per_head=True, slopes=slopes.float().to(CUDA), sinks=sinks.float().to(CUDA))
+    if kind in ("rows", "split"):
+        positions = torch.tensor(rows, dtype=torch.int32, device=CUDA)
+        chunks = 3 if kind == "split" else 0
+        scratch = torch.empty(kernels.attention_rows_scratch_floats(len(rows), heads, dv, 3), dtype=torch.float32,
+                              device=CUDA) if chunks else None
+        got = kernels.attention_rows(
+            q[rows].to(dtype).reshape(len(rows), heads * dk).to(CUDA), heads * dk, key_cache.to(CUDA), value_cache.to(CUDA),
+            table.to(CUDA), torch.zeros(len(rows), dtype=torch.int32, device=CUDA), positions, num_q=heads, num_kv=kv,
+            head_dim=dk, value_dim=dv, window=None, scale=scale, gate=gate[rows].to(dtype).to(CUDA), **extras,
+            scratch=scratch, max_chunks=chunks)
+    elif kind == "tiles":
+        # the whole prompt in tiles of up to 64 tokens, cut at odd places
+        firsts = [0, 1, 3, 50] + list(range(114, n, 64))
+        counts = [b - a for a, b in zip(firsts, firsts[1:] + [n])]
+        ints = lambda values: torch.tensor(values, dtype=torch.int32, device=CUDA)
+        out = torch.empty(n, heads * dv, dtype=dtype, device=CUDA)
+        kernels.attention_tiles(
+            q.to(dtype).reshape(n, heads * dk).to(CUDA), key_cache.to(CUDA), value_cache.to(CUDA), table.to(CUDA),
+            ints(list(range(n))), ints([0] * len(firsts)), ints(firsts), ints(counts), num_q=heads, num_kv=kv, key_dim=dk,
+            value_dim=dv, window=None, keep_first=0, scale=scale, out=out, gate=gate.to(dtype).to(CUDA), **extras)
+        got = out[rows]
+    else:
+        out = torch.empty(len(rows), heads * dv, dtype=dtype, device=CUDA)
+        need = kernels.attention_tiles_singles_floats(len(rows), heads, dv, None, 0, 704)
+        kernels.attention_tiles_singles(
+            q[rows].to(dtype).reshape(len(rows), heads * dk).to(CUDA), key_cache.to(CUDA), value_cache.to(CUDA),
+            table.to(CUDA), torch.tensor(rows, dtype=torch.int32, device=CUDA),
+            torch.zeros(len(rows), dtype=torch.int32, device=CUDA), num_q=heads, num_kv=kv, key_dim=dk, value_dim=dv,
+            window=None, keep_first=0, scale=scale, max_context=704,
+            scratch=torch.empty(need, dtype=torch.float32, device=CUDA), out=out, gate=gate[rows].to(dtype).to(CUDA),
+            **extras)
+        got = out
     # scores of a hundred and more carry float32 rounding of 1e-5 into their exponentials
     close(got.view(len(rows), heads, dv), want, dtype, scale=want.abs().max().item(),
           limit=3e-5 if dtype == torch.float32 else None)
-    # the far key carries weight: without it the first head's output at position 700 is another one
+    # the far key carries weight: it and the sink share the first head's denominator at position 700 (in
+    # bfloat16 the rounding of q moves the score by up to half a unit, and the shares with it)
     far = rows.index(700)
-    lone = torch.sigmoid(gate[700, 0]) * v[3, 0] * 0.5         # the key and the sink share the denominator
-    assert (want[far, 0] - lone).abs().max() < 0.3 * lone.abs().max()
+    alone = torch.sigmoid(gate[700, 0]) * v[3, 0]
+    share = (want[far, 0] @ alone / (alone @ alone)).item()
+    assert 0.1 < share < 0.9
+    assert (want[far, 0] - share * alone).abs().max() < 0.05 * alone.abs().max()
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("rank,rot", [(20, 4), (32, 8), (256, 64)])
+@pytest.mark.parametrize("rank,rot", [(20, 4), (32, 8), (48, 16), (256, 64)])
 def test_attention_whose_values_lie_inside_the_key_rows(rank, rot, dtype):
     """One kv head whose rows are [latent | rotated part]: the values are the first ``rank`` elements of
     the same rows; a far key stands out."""
@@ -276,15 +305,32 @@ def test_attention_whose_values_lie_inside_the_key_rows(rank, rot, dtype):
         weights = plain.causal_softmax_rows((q[:, h] @ rows_kv[:, 0].T) * scale)
         want[:, h] = (weights @ rows_kv[:, 0, :rank])[checked]
     key_cache, _, table = _paged(rows_kv, None, page, dtype, 4)
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=CUDA)
     for chunks in (0, 3):
         scratch = torch.empty(kernels.attention_rows_scratch_floats(len(checked), heads, rank, 3), dtype=torch.float32,
                               device=CUDA) if chunks else None
         got = kernels.attention_rows(
             q[checked].to(dtype).reshape(len(checked), -1).to(CUDA), heads * (rank + rot), key_cache.to(CUDA), None,
-            table.to(CUDA), torch.zeros(len(checked), dtype=torch.int32, device=CUDA),
-            torch.tensor(checked, dtype=torch.int32, device=CUDA), num_q=heads, num_kv=1, head_dim=rank + rot,
-            value_dim=rank, value_offset=0, window=None, scale=scale, scratch=scratch, max_chunks=chunks)
+            table.to(CUDA), torch.zeros(len(checked), dtype=torch.int32, device=CUDA), ints(checked), num_q=heads,
+            num_kv=1, head_dim=rank + rot, value_dim=rank, value_offset=0, window=None, scale=scale, scratch=scratch,
+            max_chunks=chunks)
         close(got.view(len(checked), heads, rank), want, dtype)
+    if dtype == torch.bfloat16 and kernels.attention_tiles_supports(rank + rot, rank, heads, 1, value_in_key=True):
+        key_cache, _, table = _paged(rows_kv, None, page, dtype, 4, fill=1e30)
+        sizes = dict(num_q=heads, num_kv=1, key_dim=rank + rot, value_dim=rank, window=None, keep_first=0, scale=scale)
+        firsts = [0, 2, 9] + list(range(73, n, 64))
+        counts = [b - a for a, b in zip(firsts, firsts[1:] + [n])]
+        out = torch.empty(n, heads * rank, dtype=dtype, device=CUDA)
+        kernels.attention_tiles(q.to(dtype).reshape(n, -1).to(CUDA), key_cache.to(CUDA), None, table.to(CUDA),
+                                ints(list(range(n))), ints([0] * len(firsts)), ints(firsts), ints(counts), **sizes, out=out)
+        close(out[checked].view(len(checked), heads, rank), want, dtype)
+        out = torch.empty(len(checked), heads * rank, dtype=dtype, device=CUDA)
+        need = kernels.attention_tiles_singles_floats(len(checked), heads, rank, None, 0, 544)
+        kernels.attention_tiles_singles(
+            q[checked].to(dtype).reshape(len(checked), -1).to(CUDA), key_cache.to(CUDA), None, table.to(CUDA),
+            ints(checked), ints([0] * len(checked)), **sizes, max_context=544,
+            scratch=torch.empty(need, dtype=torch.float32, device=CUDA), out=out)
+        close(out.view(len(checked), heads, rank), want, dtype)
     assert (want[-1, 1] - rows_kv[2, 0, :rank]).abs().max() < 0.05 * rows_kv[2, 0, :rank].abs().max()
 
 

@@ -1,7 +1,12 @@
 // Windowed attention over the paged cache on the tensor cores (bfloat16 operands, float32
 // scores, weights and sums), for mixers whose sizes are parameters: keys TILES_KEY_DIM wide,
 // values TILES_VALUE_DIM wide (both multiples of 16; the library is compiled per pair), a
-// sliding window that may keep the first `keep_first` keys visible, an optional output gate.
+// sliding window that may keep the first `keep_first` keys visible, an optional output gate (one number
+// a value, or one a head), an optional distance bias (head h takes slopes[h] * (p - j) off the score of
+// key j) and an optional sink a head (exp(sink) joins the softmax's denominator once, with no key and no
+// value).  Compiled with TILES_VALUE_IN_KEY=1 the values are the first TILES_VALUE_DIM elements of the
+// key rows themselves (attention over latents that serve as keys and values): no value cache is read
+// and the key tile in shared memory is the value tile too.
 //
 // The query at position p sees key j iff j <= p and (window == 0 or p - j < window or
 // j < keep_first).  A CTA of 4 warps holds up to 64 query rows (16 a warp) that share one
@@ -31,6 +36,10 @@
 #endif
 #ifndef TILES_VALUE_DIM
 #define TILES_VALUE_DIM 64
+#endif
+
+#ifndef TILES_VALUE_IN_KEY
+#define TILES_VALUE_IN_KEY 0
 #endif
 
 #define TL_BM 64
@@ -74,19 +83,21 @@ struct TileArgs {
     float* scratch; int window_chunks; int kept_chunks;
     int num_q, num_kv, page_size, window, keep_first;
     float scale;
+    const float* slopes; const float* sinks; int gate_per_head;
 };
 
 __device__ __forceinline__ int chunk_of_slot(int z, int window_chunks, int position, int lo, int kept);
 
 template <int KD, int VD, bool SINGLES>
 __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const TileArgs a) {
-    constexpr int KROW = KD + TL_PAD, VROW = VD + TL_PAD;
+    constexpr bool VIK = TILES_VALUE_IN_KEY != 0;
+    constexpr int KROW = KD + TL_PAD, VROW = VIK ? KROW : VD + TL_PAD;
     constexpr int KCHUNKS = KD / 8, VCHUNKS = VD / 8;
     extern __shared__ __align__(16) unsigned char shared_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(shared_raw);                         // [64][KROW]
     bf16* k_s = q_s + TL_BM * KROW;                                          // [2][32][KROW]
-    bf16* v_s = k_s + 2 * TL_BN * KROW;                                      // [2][32][VROW]
-    int* slot_s = reinterpret_cast<int*>(v_s + 2 * TL_BN * VROW);            // [2][32]
+    bf16* v_s = VIK ? k_s : k_s + 2 * TL_BN * KROW;                          // [2][32][VROW], or the key tiles
+    int* slot_s = reinterpret_cast<int*>(VIK ? k_s + 2 * TL_BN * KROW : v_s + 2 * TL_BN * VROW);   // [2][32]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = a.num_q / a.num_kv;
@@ -166,11 +177,13 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
             cp_async_16(k_s + (buffer * TL_BN + r) * KROW + c * 8,
                         a.key_cache + (int64_t)max(slot, 0) * KD + c * 8, slot >= 0);
         }
-        for (int index = tid; index < TL_BN * VCHUNKS; index += TL_WARPS * 32) {
-            const int r = index / VCHUNKS, c = index % VCHUNKS;
-            const int slot = slot_s[buffer * TL_BN + r];
-            cp_async_16(v_s + (buffer * TL_BN + r) * VROW + c * 8,
-                        a.value_cache + (int64_t)max(slot, 0) * VD + c * 8, slot >= 0);
+        if (!VIK) {
+            for (int index = tid; index < TL_BN * VCHUNKS; index += TL_WARPS * 32) {
+                const int r = index / VCHUNKS, c = index % VCHUNKS;
+                const int slot = slot_s[buffer * TL_BN + r];
+                cp_async_16(v_s + (buffer * TL_BN + r) * VROW + c * 8,
+                            a.value_cache + (int64_t)max(slot, 0) * VD + c * 8, slot >= 0);
+            }
         }
         cp_async_commit();
     };
@@ -201,6 +214,12 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
         for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.0f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
     const float scale_log2 = a.scale * TL_LOG2E;
+    // the distance bias of this thread's two rows, in the units of the scaled scores
+    const bool biased = a.slopes != nullptr;
+    const int head_a = SINGLES ? head0 + min(row_a, count - 1) : head0;
+    const int head_b = SINGLES ? head0 + min(row_b, count - 1) : head0;
+    const float slope_a = biased ? a.slopes[head_a] * TL_LOG2E : 0.0f;
+    const float slope_b = biased ? a.slopes[head_b] * TL_LOG2E : 0.0f;
 
     for (int t = 0; t < tiles; ++t) {
         const int buffer = t & 1;
@@ -248,6 +267,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
                 const int key = key0 + n * 8 + 2 * t4 + (i & 1);
                 const bool upper = i < 2;
                 float s = s_acc[n][i] * scale_log2;
+                if (biased) s -= (upper ? slope_a : slope_b) * (float)((upper ? pos_a : pos_b) - key);
                 if (!full) {
                     const int pos = upper ? pos_a : pos_b, lo = upper ? lo_a : lo_b;
                     if (!(key <= pos && (key >= lo || key < a.keep_first))) s = -INFINITY;
@@ -336,14 +356,28 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
         }
         return;
     }
-    const float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
+    float keep_a = 1.0f, keep_b = 1.0f;
+    if (a.sinks) {
+        // the sink joins the denominator: exp(sink) beside the keys' exponentials, under a common reference
+        const float sink = a.sinks[head0] * TL_LOG2E;
+        const float top_a = fmaxf(m_a, sink), top_b = fmaxf(m_b, sink);
+        keep_a = exp2f(m_a - top_a);
+        keep_b = exp2f(m_b - top_b);
+        l_a = l_a * keep_a + exp2f(sink - top_a);
+        l_b = l_b * keep_b + exp2f(sink - top_b);
+    }
+    const float inv_a = keep_a / l_a, inv_b = keep_b / l_b;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int row = half ? row_b : row_a;
         if (row >= count) continue;
-        const float inv = half ? inv_b : inv_a;
+        float inv = half ? inv_b : inv_a;
         bf16* dst = a.out + (int64_t)(first_token + row) * a.out_token_stride + (int64_t)head0 * VD;
-        const bf16* gate = a.gate ? a.gate + (int64_t)(first_token + row) * a.gate_token_stride + (int64_t)head0 * VD : nullptr;
+        const bf16* gate = nullptr;
+        if (a.gate && a.gate_per_head)
+            inv *= sigmoid_of(__bfloat162float(a.gate[(int64_t)(first_token + row) * a.gate_token_stride + head0]));
+        else if (a.gate)
+            gate = a.gate + (int64_t)(first_token + row) * a.gate_token_stride + (int64_t)head0 * VD;
 #pragma unroll
         for (int n = 0; n < VD / 8; ++n) {
             const int dim = n * 8 + 2 * t4;
@@ -376,14 +410,16 @@ __device__ __forceinline__ int chunk_of_slot(int z, int window_chunks, int posit
 // shared memory in the order of the keys and leave as one (max, sum, out) per head.
 template <int KD, int VD>
 __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_singles_kernel(const TileArgs a) {
-    constexpr int KROW = KD + TL_PAD, VROW = VD + TL_PAD;
+    constexpr bool VIK = TILES_VALUE_IN_KEY != 0;
+    constexpr int KROW = KD + TL_PAD, VROW = VIK ? KROW : VD + TL_PAD;
     constexpr int KCHUNKS = KD / 8, VCHUNKS = VD / 8;
     static_assert(TL_CHUNK == TL_WARPS * TL_BN, "a warp takes one tile of the chunk");
+    static_assert(!VIK || VD <= KD, "values inside the key rows are no longer than the rows");
     extern __shared__ __align__(16) unsigned char shared_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(shared_raw);                         // [16][KROW]
     bf16* k_s = q_s + 16 * KROW;                                             // [chunk][KROW]
-    bf16* v_s = k_s + TL_CHUNK * KROW;                                       // [chunk][VROW]
-    int* slot_s = reinterpret_cast<int*>(v_s + TL_CHUNK * VROW);             // [chunk]
+    bf16* v_s = VIK ? k_s : k_s + TL_CHUNK * KROW;                           // [chunk][VROW], or the keys
+    int* slot_s = reinterpret_cast<int*>(VIK ? k_s + TL_CHUNK * KROW : v_s + TL_CHUNK * VROW);   // [chunk]
     float* part_s = reinterpret_cast<float*>(k_s);                           // over K and V once they are used up
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -418,10 +454,12 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_singles_kernel(con
         const int slot = slot_s[r];
         cp_async_16(k_s + r * KROW + c * 8, a.key_cache + (int64_t)max(slot, 0) * KD + c * 8, slot >= 0);
     }
-    for (int index = tid; index < TL_CHUNK * VCHUNKS; index += TL_WARPS * 32) {
-        const int r = index / VCHUNKS, c = index % VCHUNKS;
-        const int slot = slot_s[r];
-        cp_async_16(v_s + r * VROW + c * 8, a.value_cache + (int64_t)max(slot, 0) * VD + c * 8, slot >= 0);
+    if (!VIK) {
+        for (int index = tid; index < TL_CHUNK * VCHUNKS; index += TL_WARPS * 32) {
+            const int r = index / VCHUNKS, c = index % VCHUNKS;
+            const int slot = slot_s[r];
+            cp_async_16(v_s + r * VROW + c * 8, a.value_cache + (int64_t)max(slot, 0) * VD + c * 8, slot >= 0);
+        }
     }
     cp_async_commit();
     cp_async_wait<0>();
@@ -461,12 +499,16 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_singles_kernel(con
             }
         }
         const float scale_log2 = a.scale * TL_LOG2E;
+        const bool biased = a.slopes != nullptr;
+        const float slope_a = biased ? a.slopes[head0 + min(g, group - 1)] * TL_LOG2E : 0.0f;
+        const float slope_b = biased ? a.slopes[head0 + min(g + 8, group - 1)] * TL_LOG2E : 0.0f;
 #pragma unroll
         for (int n = 0; n < TL_BN / 8; ++n) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = tile_key + n * 8 + 2 * t4 + (i & 1);
                 float s = s_acc[n][i] * scale_log2;
+                if (biased) s -= (i < 2 ? slope_a : slope_b) * (float)(position - key);
                 if (!(key <= position && (key >= lo || key < kept))) s = -INFINITY;
                 s_acc[n][i] = s;
                 if (i < 2) m_a = fmaxf(m_a, s); else m_b = fmaxf(m_b, s);
@@ -598,8 +640,17 @@ __global__ void merge_singles_kernel(const TileArgs a, int tokens) {
             if (dim < VD) o[j] += src[2 + dim] * weight;
         }
     }
-    const float inv = 1.0f / l;
-    const bf16* gate = a.gate ? a.gate + (int64_t)token * a.gate_token_stride + (int64_t)head * VD : nullptr;
+    float keep = 1.0f;
+    if (a.sinks) {
+        const float sink = a.sinks[head] * TL_LOG2E;
+        const float both = fmaxf(top, sink);
+        keep = exp2f(top - both);
+        l = l * keep + exp2f(sink - both);
+    }
+    float inv = keep / l;
+    const bf16* gate = nullptr;
+    if (a.gate && a.gate_per_head) inv *= sigmoid_of(__bfloat162float(a.gate[(int64_t)token * a.gate_token_stride + head]));
+    else if (a.gate) gate = a.gate + (int64_t)token * a.gate_token_stride + (int64_t)head * VD;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
         const int dim = lane + 32 * i;
@@ -616,34 +667,40 @@ extern "C" int tvb_attention_tiles_value_dim() { return TILES_VALUE_DIM; }
 extern "C" int tvb_attention_tiles_tile_tokens() { return TL_BM; }
 extern "C" int tvb_attention_tiles_chunk_keys() { return TL_CHUNK; }
 
+extern "C" int tvb_attention_tiles_value_in_key() { return TILES_VALUE_IN_KEY; }
+
 static size_t tiles_shared_bytes() {
     return (size_t)(TL_BM + 2 * TL_BN) * (TILES_KEY_DIM + TL_PAD) * sizeof(bf16) +
-           (size_t)2 * TL_BN * (TILES_VALUE_DIM + TL_PAD) * sizeof(bf16) + 2 * TL_BN * sizeof(int);
+           (TILES_VALUE_IN_KEY ? 0 : (size_t)2 * TL_BN * (TILES_VALUE_DIM + TL_PAD) * sizeof(bf16)) +
+           2 * TL_BN * sizeof(int);
 }
 
 static int check_common(const TileArgs& a, int key_dim, int value_dim) {
     if (key_dim != TILES_KEY_DIM || value_dim != TILES_VALUE_DIM || TILES_KEY_DIM % 16 || TILES_VALUE_DIM % 16 ||
         a.num_q <= 0 || a.num_kv <= 0 || a.num_q % a.num_kv || a.page_size <= 0 || a.window < 0 || a.keep_first < 0 ||
         (a.q_token_stride * 2) % 16 || ((uintptr_t)a.q) % 16 || a.out_token_stride % 2 || ((uintptr_t)a.out) % 4 ||
-        (a.gate && (a.gate_token_stride % 2 || ((uintptr_t)a.gate) % 4)))
+        (a.gate && !a.gate_per_head && (a.gate_token_stride % 2 || ((uintptr_t)a.gate) % 4)) ||
+        (!TILES_VALUE_IN_KEY && !a.value_cache) || (TILES_VALUE_IN_KEY && TILES_VALUE_DIM > TILES_KEY_DIM))
         return TVB_BAD_ARGUMENT;
     return 0;
 }
 
 // Prompt portions: tile i holds tile_count[i] (1..64) consecutive tokens from flat index tile_first[i]
 // on, of the request in row tile_row[i] of block_tables.
-extern "C" int tvb_attention_tiles(const void* q, long long q_token_stride, const void* key_cache,
-                                   const void* value_cache, const int* block_tables, int table_stride,
-                                   const int* positions, const int* tile_row, const int* tile_first,
-                                   const int* tile_count, void* out, long long out_token_stride, const void* gate,
-                                   long long gate_token_stride, int tiles, int num_q, int num_kv, int key_dim,
-                                   int value_dim, int page_size, int window, int keep_first, float scale,
-                                   void* stream) {
+// `slopes` and `sinks`: float32 [num_q] or null; `gate_per_head`: the gate holds one number a head.
+extern "C" int tvb_attention_tiles_biased(const void* q, long long q_token_stride, const void* key_cache,
+                                          const void* value_cache, const int* block_tables, int table_stride,
+                                          const int* positions, const int* tile_row, const int* tile_first,
+                                          const int* tile_count, void* out, long long out_token_stride,
+                                          const void* gate, long long gate_token_stride, int gate_per_head,
+                                          const float* slopes, const float* sinks, int tiles, int num_q, int num_kv,
+                                          int key_dim, int value_dim, int page_size, int window, int keep_first,
+                                          float scale, void* stream) {
     if (tiles <= 0) return 0;
     TileArgs a{(const bf16*)q, q_token_stride, (const bf16*)key_cache, (const bf16*)value_cache, block_tables,
                table_stride, positions, nullptr, tile_row, tile_first, tile_count, (bf16*)out, out_token_stride,
                (const bf16*)gate, gate_token_stride, nullptr, 0, 0, num_q, num_kv, page_size, window,
-               window > 0 ? keep_first : 0, scale};
+               window > 0 ? keep_first : 0, scale, slopes, sinks, gate_per_head};
     if (check_common(a, key_dim, value_dim) || num_q > 65535) return TVB_BAD_ARGUMENT;
     auto kernel = attention_tiles_kernel<TILES_KEY_DIM, TILES_VALUE_DIM, false>;
     const size_t shared = tiles_shared_bytes();
@@ -651,6 +708,19 @@ extern "C" int tvb_attention_tiles(const void* q, long long q_token_stride, cons
     if (e != cudaSuccess) return (int)e;
     kernel<<<dim3(tiles, num_q), TL_WARPS * 32, shared, (cudaStream_t)stream>>>(a);
     return tvb_last_error();
+}
+
+extern "C" int tvb_attention_tiles(const void* q, long long q_token_stride, const void* key_cache,
+                                   const void* value_cache, const int* block_tables, int table_stride,
+                                   const int* positions, const int* tile_row, const int* tile_first,
+                                   const int* tile_count, void* out, long long out_token_stride, const void* gate,
+                                   long long gate_token_stride, int tiles, int num_q, int num_kv, int key_dim,
+                                   int value_dim, int page_size, int window, int keep_first, float scale,
+                                   void* stream) {
+    return tvb_attention_tiles_biased(q, q_token_stride, key_cache, value_cache, block_tables, table_stride, positions,
+                                      tile_row, tile_first, tile_count, out, out_token_stride, gate, gate_token_stride,
+                                      0, nullptr, nullptr, tiles, num_q, num_kv, key_dim, value_dim, page_size, window,
+                                      keep_first, scale, stream);
 }
 
 // How many chunk slots a row of the singles form has: (for the window, for kept first keys).
@@ -671,18 +741,19 @@ extern "C" long long tvb_attention_tiles_singles_floats(int tokens, int num_q, i
 
 // Single tokens (decoded ones): token i is of the request in row token_row[i] (-1: padding) at
 // positions[i] < max_context; its keys and values are in the cache already.
-extern "C" int tvb_attention_tiles_singles(const void* q, long long q_token_stride, const void* key_cache,
-                                           const void* value_cache, const int* block_tables, int table_stride,
-                                           const int* positions, const int* token_row, void* out,
-                                           long long out_token_stride, const void* gate, long long gate_token_stride,
-                                           float* scratch, int tokens, int num_q, int num_kv, int key_dim,
-                                           int value_dim, int page_size, int window, int keep_first, float scale,
-                                           int max_context, void* stream) {
+extern "C" int tvb_attention_tiles_singles_biased(const void* q, long long q_token_stride, const void* key_cache,
+                                                  const void* value_cache, const int* block_tables, int table_stride,
+                                                  const int* positions, const int* token_row, void* out,
+                                                  long long out_token_stride, const void* gate,
+                                                  long long gate_token_stride, int gate_per_head, const float* slopes,
+                                                  const float* sinks, float* scratch, int tokens, int num_q,
+                                                  int num_kv, int key_dim, int value_dim, int page_size, int window,
+                                                  int keep_first, float scale, int max_context, void* stream) {
     if (tokens <= 0) return 0;
     TileArgs a{(const bf16*)q, q_token_stride, (const bf16*)key_cache, (const bf16*)value_cache, block_tables,
                table_stride, positions, token_row, nullptr, nullptr, nullptr, (bf16*)out, out_token_stride,
                (const bf16*)gate, gate_token_stride, scratch, 0, 0, num_q, num_kv, page_size, window,
-               window > 0 ? keep_first : 0, scale};
+               window > 0 ? keep_first : 0, scale, slopes, sinks, gate_per_head};
     if (check_common(a, key_dim, value_dim) || !scratch || max_context <= 0 || num_q / num_kv > TL_BM || num_kv > 65535)
         return TVB_BAD_ARGUMENT;
     singles_chunks(a.window, a.keep_first, max_context, &a.window_chunks, &a.kept_chunks);
@@ -692,7 +763,8 @@ extern "C" int tvb_attention_tiles_singles(const void* q, long long q_token_stri
     if (num_q / num_kv <= 16) {
         auto kernel = attention_singles_kernel<TILES_KEY_DIM, TILES_VALUE_DIM>;
         const size_t shared = (size_t)(16 + TL_CHUNK) * (TILES_KEY_DIM + TL_PAD) * sizeof(bf16) +
-                              (size_t)TL_CHUNK * (TILES_VALUE_DIM + TL_PAD) * sizeof(bf16) + TL_CHUNK * sizeof(int);
+                              (TILES_VALUE_IN_KEY ? 0 : (size_t)TL_CHUNK * (TILES_VALUE_DIM + TL_PAD) * sizeof(bf16)) +
+                              TL_CHUNK * sizeof(int);
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (e != cudaSuccess) return (int)e;
         kernel<<<grid, TL_WARPS * 32, shared, s>>>(a);
@@ -706,4 +778,17 @@ extern "C" int tvb_attention_tiles_singles(const void* q, long long q_token_stri
     const int64_t rows = (int64_t)tokens * num_q;
     merge_singles_kernel<TILES_VALUE_DIM><<<(unsigned)((rows + TL_WARPS - 1) / TL_WARPS), TL_WARPS * 32, 0, s>>>(a, tokens);
     return tvb_last_error();
+}
+
+extern "C" int tvb_attention_tiles_singles(const void* q, long long q_token_stride, const void* key_cache,
+                                           const void* value_cache, const int* block_tables, int table_stride,
+                                           const int* positions, const int* token_row, void* out,
+                                           long long out_token_stride, const void* gate, long long gate_token_stride,
+                                           float* scratch, int tokens, int num_q, int num_kv, int key_dim,
+                                           int value_dim, int page_size, int window, int keep_first, float scale,
+                                           int max_context, void* stream) {
+    return tvb_attention_tiles_singles_biased(q, q_token_stride, key_cache, value_cache, block_tables, table_stride,
+                                              positions, token_row, out, out_token_stride, gate, gate_token_stride, 0,
+                                              nullptr, nullptr, scratch, tokens, num_q, num_kv, key_dim, value_dim,
+                                              page_size, window, keep_first, scale, max_context, stream);
 }

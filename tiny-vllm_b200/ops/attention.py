@@ -306,7 +306,8 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
     gate = projected[:, g_at:g_at + mixer.gate_cols] if mixer.gate else None
     queries = projected[:, q_at:q_at + mixer.q_cols]
     heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, key_dim=mixer.key_dim,
-                 value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale)
+                 value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale,
+                 gate_per_head=mixer.gate == "head", slopes=mixer.slopes, sinks=mixer.sinks)
     if windowed_on_tensor_cores(mixer, projected, q_at, g_at, out):
         # bfloat16: prompt portions in tiles of 64 tokens, single tokens (decoded ones, whose keys are in the
         # cache by now) one CTA per kv head and chunk of keys
@@ -369,13 +370,38 @@ def latent_attention(ctx, mixer, projected: torch.Tensor, run: int) -> torch.Ten
     kernels.head_product(q[:, :, :mixer.key_dim], mixer.uk_by_head, folded[:, :, :rank])
     if rot > 0:
         kernels.rotate_heads(q[:, :, mixer.key_dim:], folded[:, :, rank:], inv_freq, magnitude, ctx.positions)
-    scratch = None
-    if ctx.split_chunks > 0:
-        scratch = ctx.workspace(kernels.attention_rows_scratch_floats(tokens, heads, rank, ctx.split_chunks))
-    attended = kernels.attention_rows(
-        folded, folded.stride(0), keys, None, ctx.block_tables[group], ctx.token_row, ctx.positions,
-        num_q=heads, num_kv=1, head_dim=rank + rot, value_dim=rank, value_offset=0, window=None,
-        scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks)
+    attended = None
+    queries = folded.view(tokens, heads * (rank + rot))
+    if (projected.dtype == torch.bfloat16 and TENSOR_CORE_WINDOWS and (ctx.decode_only or ctx.tile_row is not None)
+            and kernels.attention_tiles_supports(rank + rot, rank, heads, 1, value_in_key=True)):
+        # bfloat16: prompt portions in tiles of 64 tokens a head, single tokens one CTA a chunk of keys for all
+        # heads at once (the cached rows are read once a token); the key tile in shared memory is the value tile
+        attended = torch.empty((tokens, heads * rank), dtype=projected.dtype, device=projected.device)
+        sizes = dict(num_q=heads, num_kv=1, key_dim=rank + rot, value_dim=rank, window=None, keep_first=0,
+                     scale=mixer.scale)
+
+        def singles(part):
+            need = kernels.attention_tiles_singles_floats(part.stop - part.start, heads, rank, None, 0, ctx.max_context)
+            kernels.attention_tiles_singles(
+                queries[part], keys, None, ctx.block_tables[group], ctx.positions[part], ctx.token_row[part], **sizes,
+                max_context=ctx.max_context, scratch=ctx.workspace(need), out=attended[part])
+
+        if ctx.decode_only:
+            singles(slice(0, tokens))
+        else:
+            if ctx.tile_row.shape[0] > 0:
+                kernels.attention_tiles(queries, keys, None, ctx.block_tables[group], ctx.positions, ctx.tile_row,
+                                        ctx.tile_first, ctx.tile_count, **sizes, out=attended)
+            for first, count in ctx.single_runs:
+                singles(slice(first, first + count))
+    if attended is None:
+        scratch = None
+        if ctx.split_chunks > 0:
+            scratch = ctx.workspace(kernels.attention_rows_scratch_floats(tokens, heads, rank, ctx.split_chunks))
+        attended = kernels.attention_rows(
+            queries, queries.stride(0), keys, None, ctx.block_tables[group], ctx.token_row, ctx.positions,
+            num_q=heads, num_kv=1, head_dim=rank + rot, value_dim=rank, value_offset=0, window=None,
+            scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks)
     gated = torch.empty((tokens, heads, mixer.value_dim), dtype=projected.dtype, device=projected.device)
     gate = projected[:, mixer.q_rank + rank + rot:] if mixer.gate else None
     kernels.head_product(attended.view(tokens, heads, rank), mixer.uv_by_head, gated, gate=gate)
@@ -385,7 +411,7 @@ def latent_attention(ctx, mixer, projected: torch.Tensor, run: int) -> torch.Ten
 def windowed_on_tensor_cores(mixer, projected: torch.Tensor, q_at: int, g_at: int, out: torch.Tensor) -> bool:
     """Whether the tensor-core kernels take this mixer's attention: bfloat16, key and value sizes
     that are multiples of 16, 16-byte aligned query rows; everything else goes to the row kernel."""
-    return (projected.dtype == torch.bfloat16 and TENSOR_CORE_WINDOWS and getattr(mixer, "plain", True)
+    return (projected.dtype == torch.bfloat16 and TENSOR_CORE_WINDOWS
             and kernels.attention_tiles_supports(mixer.key_dim, mixer.value_dim, mixer.num_heads, mixer.num_kv_heads)
             and projected.stride(0) % 8 == 0 and q_at % 8 == 0 and projected.data_ptr() % 16 == 0
-            and g_at % 2 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)
+            and (g_at % 2 == 0 or mixer.gate == "head") and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)

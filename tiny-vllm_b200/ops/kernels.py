@@ -727,14 +727,24 @@ def qkv_prepare(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, num_q: i
 TILES_CHUNK_KEYS = 128
 
 
-def _tiles_library(key_dim: int, value_dim: int) -> str:
+def _tiles_library(key_dim: int, value_dim: int, value_in_key: bool = False) -> str:
     from .build import variant
+    if value_in_key:
+        return variant("attention_tiles", TILES_KEY_DIM=key_dim, TILES_VALUE_DIM=value_dim, TILES_VALUE_IN_KEY=1)
     return variant("attention_tiles", TILES_KEY_DIM=key_dim, TILES_VALUE_DIM=value_dim)
 
 
-def attention_tiles_supports(key_dim: int, value_dim: int, num_q: int, num_kv: int) -> bool:
-    """Key and value sizes that are multiples of 16 (up to 256), whole groups of up to 64 q heads."""
-    return (key_dim % 16 == 0 and value_dim % 16 == 0 and 0 < key_dim <= 256 and 0 < value_dim <= 256
+# largest key size with values inside the key rows: the value tile is the key tile, so shared memory holds one
+TILES_MAX_DIM, TILES_MAX_DIM_VALUE_IN_KEY = 256, 320
+
+
+def attention_tiles_supports(key_dim: int, value_dim: int, num_q: int, num_kv: int, *,
+                             value_in_key: bool = False) -> bool:
+    """Key and value sizes that are multiples of 16 (up to 256; keys up to 320 where the values lie inside
+    the key rows), whole groups of up to 64 q heads."""
+    key_limit = TILES_MAX_DIM_VALUE_IN_KEY if value_in_key else TILES_MAX_DIM
+    return (key_dim % 16 == 0 and value_dim % 16 == 0 and 0 < key_dim <= key_limit and 0 < value_dim <= TILES_MAX_DIM
+            and (not value_in_key or value_dim <= key_dim)
             and num_kv > 0 and num_q % num_kv == 0 and num_q // num_kv <= PREFILL_TILE_TOKENS)
 
 
@@ -751,78 +761,102 @@ def attention_tiles_singles_floats(tokens: int, num_q: int, value_dim: int, wind
     return tokens * num_q * _tiles_window_chunks(window, keep_first if window else 0, max_context) * (value_dim + 2)
 
 
-def _tiles_common(name, q, key_cache, value_cache, out, gate, num_q, num_kv, key_dim, value_dim, tokens):
-    if q.dtype != torch.bfloat16 or key_cache.dtype != torch.bfloat16 or value_cache.dtype != torch.bfloat16:
+def _tiles_common(name, q, key_cache, value_cache, out, gate, num_q, num_kv, key_dim, value_dim, tokens,
+                  gate_per_head=False, slopes=None, sinks=None):
+    """Checks of both tile kernels; returns whether the values lie inside the key rows (no value cache)."""
+    value_in_key = value_cache is None
+    if q.dtype != torch.bfloat16 or key_cache.dtype != torch.bfloat16 or \
+            (value_cache is not None and value_cache.dtype != torch.bfloat16):
         raise KernelError(f"{name} is a bfloat16 kernel")
-    if not attention_tiles_supports(key_dim, value_dim, num_q, num_kv):
+    if not attention_tiles_supports(key_dim, value_dim, num_q, num_kv, value_in_key=value_in_key):
         raise KernelError(f"{name} does not take key size {key_dim}, value size {value_dim}, {num_q}/{num_kv} heads")
     if key_cache.dim() != 4 or (key_cache.shape[1], key_cache.shape[3]) != (num_kv, key_dim) or \
-            value_cache.shape != key_cache.shape[:3] + (value_dim,) or not key_cache.is_contiguous() or \
-            not value_cache.is_contiguous():
+            not key_cache.is_contiguous() or (value_cache is not None and (
+                value_cache.shape != key_cache.shape[:3] + (value_dim,) or not value_cache.is_contiguous())):
         raise KernelError(f"{name}: caches must be contiguous [pages, num_kv, page_size, key / value size]")
     if q.dim() != 2 or q.stride(1) != 1 or q.stride(0) % 8 or q.data_ptr() % 16 or q.shape[1] < num_q * key_dim:
         raise KernelError(f"{name}: q must be [tokens, >= num_q * key_dim] with 16-byte aligned rows")
-    for label, t in (("out", out), ("gate", gate)):
-        if t is not None and (t.shape != (tokens, num_q * value_dim) or t.dtype != torch.bfloat16
-                              or t.stride(1) != 1 or t.stride(0) % 2 or t.data_ptr() % 4):
-            raise KernelError(f"{name}: {label} must be bfloat16 [tokens, num_q * value_dim] with rows of an even stride")
+    if out is None or out.shape != (tokens, num_q * value_dim) or out.dtype != torch.bfloat16 or out.stride(1) != 1 \
+            or out.stride(0) % 2 or out.data_ptr() % 4:
+        raise KernelError(f"{name}: out must be bfloat16 [tokens, num_q * value_dim] with rows of an even stride")
+    if gate is not None and gate_per_head:
+        if gate.shape != (tokens, num_q) or gate.dtype != torch.bfloat16 or gate.stride(1) != 1:
+            raise KernelError(f"{name}: a gate of one number a head is bfloat16 [tokens, num_q]")
+    elif gate is not None and (gate.shape != (tokens, num_q * value_dim) or gate.dtype != torch.bfloat16
+                               or gate.stride(1) != 1 or gate.stride(0) % 2 or gate.data_ptr() % 4):
+        raise KernelError(f"{name}: gate must be bfloat16 [tokens, num_q * value_dim] with rows of an even stride")
+    for label, t in (("slopes", slopes), ("sinks", sinks)):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (num_q,) or not t.is_contiguous()):
+            raise KernelError(f"{name}: {label} must be contiguous float32 [num_q]")
+    return value_in_key
 
 
-def attention_tiles(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+def attention_tiles(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor | None,
                     block_tables: torch.Tensor, positions: torch.Tensor, tile_row: torch.Tensor,
                     tile_first: torch.Tensor, tile_count: torch.Tensor, *, num_q: int, num_kv: int,
                     key_dim: int, value_dim: int, window: int | None, keep_first: int, scale: float,
-                    out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor, gate: torch.Tensor | None = None, gate_per_head: bool = False,
+                    slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Windowed paged attention on the tensor cores for tiles of up to 64 consecutive query tokens of
     one request (bfloat16; float32 scores, weights and sums).  ``q`` [tokens, >= num_q * key_dim]
     (rows may be strided) holds prepared queries; tile i holds ``tile_count[i]`` tokens from flat
     index ``tile_first[i]`` on of request row ``tile_row[i]``.  With a window the first
-    ``keep_first`` keys stay visible.  ``gate``: the output is multiplied by sigmoid(gate)."""
-    _need_cuda(q, key_cache, value_cache, block_tables, positions, tile_row, tile_first, tile_count, out, gate)
+    ``keep_first`` keys stay visible.  ``gate``: the output is multiplied by sigmoid(gate), one number a
+    value or (``gate_per_head``, [tokens, num_q]) one a head.  ``slopes`` (float32 [num_q]): slope *
+    (position - j) is taken off the score of key j; ``sinks`` (float32 [num_q]): exp(sink) joins the
+    denominator once.  ``value_cache=None``: the values are the first ``value_dim`` elements of the key
+    rows."""
+    _need_cuda(q, key_cache, value_cache, block_tables, positions, tile_row, tile_first, tile_count, out, gate,
+               slopes, sinks)
     tokens, tiles = positions.shape[0], tile_row.shape[0]
-    _tiles_common("attention_tiles", q, key_cache, value_cache, out, gate, num_q, num_kv, key_dim, value_dim, tokens)
+    value_in_key = _tiles_common("attention_tiles", q, key_cache, value_cache, out, gate, num_q, num_kv, key_dim,
+                                 value_dim, tokens, gate_per_head, slopes, sinks)
     for t in (block_tables, positions, tile_row, tile_first, tile_count):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("attention_tiles: index tensors must be contiguous int32")
-    library = _tiles_library(key_dim, value_dim)
+    library = _tiles_library(key_dim, value_dim, value_in_key)
     if _fn_of(library, "tvb_attention_tiles_tile_tokens", [])() != PREFILL_TILE_TOKENS:
         raise KernelError("attention_tiles: the library's tile size is not the one steps are cut for")
-    fn = _fn_of(library, "tvb_attention_tiles",
+    fn = _fn_of(library, "tvb_attention_tiles_biased",
                 [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                 c_void_p, c_longlong, c_void_p, c_longlong] + [c_int] * 8 + [c_float, c_void_p])
-    _check(fn(q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(), block_tables.data_ptr(),
+                 c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p] + [c_int] * 8
+                + [c_float, c_void_p])
+    _check(fn(q.data_ptr(), q.stride(0), key_cache.data_ptr(), _ptr(value_cache), block_tables.data_ptr(),
               block_tables.shape[1], positions.data_ptr(), tile_row.data_ptr(), tile_first.data_ptr(),
               tile_count.data_ptr(), out.data_ptr(), out.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
+              1 if gate_per_head else 0, _ptr(slopes), _ptr(sinks),
               tiles, num_q, num_kv, key_dim, value_dim, key_cache.shape[2], window or 0, keep_first if window else 0,
               scale, _stream()), "attention_tiles")
     return out
 
 
-def attention_tiles_singles(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+def attention_tiles_singles(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor | None,
                             block_tables: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor, *,
                             num_q: int, num_kv: int, key_dim: int, value_dim: int, window: int | None,
                             keep_first: int, scale: float, max_context: int, scratch: torch.Tensor,
-                            out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+                            out: torch.Tensor, gate: torch.Tensor | None = None, gate_per_head: bool = False,
+                            slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """The same attention for single tokens whose keys and values are in the cache already (decoded
     tokens): a CTA serves the q heads of one kv head over one chunk of 128 keys, a second launch
     merges a row's chunks.  Token i is of request row ``token_row[i]`` (-1: padding, zeros come out)
     at ``positions[i]`` < ``max_context``; ``scratch``: float32, :func:`attention_tiles_singles_floats`."""
-    _need_cuda(q, key_cache, value_cache, block_tables, positions, token_row, out, gate, scratch)
+    _need_cuda(q, key_cache, value_cache, block_tables, positions, token_row, out, gate, scratch, slopes, sinks)
     tokens = positions.shape[0]
-    _tiles_common("attention_tiles_singles", q, key_cache, value_cache, out, gate, num_q, num_kv, key_dim,
-                  value_dim, tokens)
+    value_in_key = _tiles_common("attention_tiles_singles", q, key_cache, value_cache, out, gate, num_q, num_kv,
+                                 key_dim, value_dim, tokens, gate_per_head, slopes, sinks)
     for t in (block_tables, positions, token_row):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("attention_tiles_singles: index tensors must be contiguous int32")
     need = attention_tiles_singles_floats(tokens, num_q, value_dim, window, keep_first, max_context)
     if scratch.dtype != torch.float32 or scratch.numel() < need:
         raise KernelError(f"attention_tiles_singles needs {need} float32 of scratch")
-    fn = _fn_of(_tiles_library(key_dim, value_dim), "tvb_attention_tiles_singles",
+    fn = _fn_of(_tiles_library(key_dim, value_dim, value_in_key), "tvb_attention_tiles_singles_biased",
                 [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
-                 c_void_p, c_longlong, c_void_p] + [c_int] * 8 + [c_float, c_int, c_void_p])
-    _check(fn(q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(), block_tables.data_ptr(),
+                 c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_int, c_void_p])
+    _check(fn(q.data_ptr(), q.stride(0), key_cache.data_ptr(), _ptr(value_cache), block_tables.data_ptr(),
               block_tables.shape[1], positions.data_ptr(), token_row.data_ptr(), out.data_ptr(), out.stride(0),
-              _ptr(gate), 0 if gate is None else gate.stride(0), scratch.data_ptr(), tokens, num_q, num_kv, key_dim,
+              _ptr(gate), 0 if gate is None else gate.stride(0), 1 if gate_per_head else 0, _ptr(slopes), _ptr(sinks),
+              scratch.data_ptr(), tokens, num_q, num_kv, key_dim,
               value_dim, key_cache.shape[2], window or 0, keep_first if window else 0, scale, max_context,
               _stream()), "attention_tiles_singles", 2)
     return out

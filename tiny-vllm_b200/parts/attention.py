@@ -354,7 +354,9 @@ class LatentAttention(Part):
         return False
 
     def scratch_floats(self, rows: int, chunks: int) -> int:
-        return kernels.attention_rows_scratch_floats(rows, self.num_heads, self.kv_rank, chunks)
+        span = chunks * kernels.attention_chunk_keys()
+        return max(kernels.attention_rows_scratch_floats(rows, self.num_heads, self.kv_rank, chunks),
+                   kernels.attention_tiles_singles_floats(rows, self.num_heads, self.kv_rank, None, 0, span))
 
     def forward(self, x, ctx, run: int):
         projected = linear(x, self.in_weight)
