@@ -883,6 +883,208 @@ def gumapel_workload(args) -> int:
     return 0
 
 
+# ------------------------------------------------------------- Kelasun beside the dense Qwen3
+KELASUN_SIZES = {
+    # width, q heads, kv heads, head size, active feed-forward width (the layers of the 0.6B, 8B and 32B
+    # sizes); latent layers: heads of head/2 plain + 64 rotated dimensions, latents as below
+    "0.6b": (1024, 16, 8, 128, 3072),
+    "8b": (4096, 32, 8, 128, 12288),
+    "32b": (5120, 64, 8, 128, 25600),
+}
+KELASUN_LATENTS = {"0.6b": (384, 192), "8b": (1536, 256), "32b": (1536, 256)}     # q_rank, kv_rank
+KELASUN_ROT, KELASUN_EXPERTS, KELASUN_TOP = 64, 8, 2
+KELASUN_LIKE = (
+    ("post_layer_norm", "rms_norm", "norm + residual sum"),
+    ("projection_norm", "qk_norm_rope_store", "q/k norm (+ temperature; the dense model also rotates and stores)"),
+    ("qkv_prepare", "qk_norm_rope_store", "cache write"),
+    ("latent_prepare", "qk_norm_rope_store", "latent norms, rotation, cache write"),
+    ("rotate_heads", "qk_norm_rope_store", "rotation of the queries' rotated part"),
+    ("head_product", None, "up-projections a head (folded into q, applied to the attended latent)"),
+    ("attention_tiles", "attention_prefill_tc", "prompt attention"),
+    ("attention_tiles_singles", "attention_decode", "decode attention"),
+    ("route_act", "silu_mul", "routing + activation"),
+)
+
+
+def kelasun_config(size: str, layers: int):
+    from tinyvllm_b200.models import KelasunConfig
+    from tinyvllm_b200.models.kelasun import KelasunExperts, KelasunLayer
+
+    width, heads, kv, dim, ff = KELASUN_SIZES[size]
+    q_rank, kv_rank = KELASUN_LATENTS[size]
+    unit = ff // (KELASUN_TOP + 1)            # the chosen experts and the shared one together are as wide as the dense ff
+    experts = KelasunExperts(KELASUN_EXPERTS, KELASUN_TOP, unit, ff - KELASUN_TOP * unit)
+    made = []
+    for index in range(layers):
+        if index % 2 == 0:
+            made.append(KelasunLayer(type="attention", heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                     q_temp=(0.5, 256), mlp=experts))
+        else:
+            made.append(KelasunLayer(type="latent_attention", heads=heads, dim=dim // 2, vdim=dim, scale=dim ** -0.5,
+                                     q_rank=q_rank, kv_rank=kv_rank, rot_dim=KELASUN_ROT, rot_base=250000.0,
+                                     rot_scaling=(4.0, 2048.0, 32.0, 1.0), mlp=experts))
+    return KelasunConfig(vocab=MODEL["vocab_size"], width=width, norm_eps=1e-5, postln_alpha=2.5, logit_scale=1.0,
+                         layers=tuple(made))
+
+
+def dense_qwen3_config(size: str, layers: int):
+    from tinyvllm_b200.models import Qwen3Config
+
+    width, heads, kv, dim, ff = KELASUN_SIZES[size]
+    return Qwen3Config(**{**MODELS["0.6b"], "hidden_size": width, "num_attention_heads": heads,
+                          "num_key_value_heads": kv, "head_dim": dim, "intermediate_size": ff,
+                          "num_hidden_layers": layers, "tie_word_embeddings": False})
+
+
+def kelasun_roofline(name: str, kind: str, size: str, tokens: int, context: int, peak: dict):
+    """(microseconds at the measured peaks, what bounds it) of one call of kernel ``name`` in a layer of
+    ``kind`` ("attention", "latent", "dense": the Qwen3 layer): ``tokens`` new tokens whose requests hold
+    ``context`` tokens each (a prompt: context == tokens)."""
+    width, heads, kv, dim, ff = KELASUN_SIZES[size]
+    q_rank, kv_rank = KELASUN_LATENTS[size]
+    row, rot = kv_rank + KELASUN_ROT, KELASUN_ROT
+    unit = ff // (KELASUN_TOP + 1)
+    columns = KELASUN_EXPERTS * unit + (ff - KELASUN_TOP * unit)
+    pairs = tokens * (tokens + 1) // 2 if context == tokens else tokens * context
+    bytes_, flops = 0.0, 0.0
+    if name == "post_layer_norm":
+        bytes_ = tokens * width * (4 + 4 + 4 + 2)
+    elif name == "rms_norm":
+        bytes_ = tokens * width * 2 * 4
+    elif name == "projection_norm":
+        bytes_ = tokens * (heads + kv) * dim * 2 * 2
+    elif name in ("qkv_prepare", "qk_norm_rope_store"):
+        bytes_ = tokens * dim * 2 * ((heads + 2 * kv) + heads + 2 * kv) if name == "qk_norm_rope_store" \
+            else tokens * dim * 2 * 2 * 2 * kv
+    elif name == "latent_prepare":
+        bytes_ = tokens * (q_rank + row) * 2 * 2
+    elif name == "rotate_heads":
+        bytes_ = tokens * heads * rot * 2 * 2
+    elif name == "head_product":
+        flops = 2.0 * tokens * heads * kv_rank * (dim // 2 + dim) / 2      # the two products of a layer, averaged
+    elif name in ("route_act",):
+        bytes_ = tokens * columns * 2 * 2
+    elif name == "silu_mul":
+        bytes_ = tokens * ff * 2 * 3
+    elif name in ("attention_tiles", "attention_prefill_tc", "attention_prefill"):
+        flops = 2.0 * heads * ((row + kv_rank) if kind == "latent" else 2 * dim) * pairs
+    elif name in ("attention_tiles_singles", "attention_decode"):
+        bytes_ = tokens * context * 2 * (row if kind == "latent" else kv * 2 * dim)
+    if flops:
+        return flops / (peak["bf16_tflops"] * 1e12) * 1e6, "tensor"
+    return bytes_ / (peak["hbm_gbs"] * 1e9) * 1e6, "memory"
+
+
+def kelasun_workload(args) -> int:
+    """Prefill and decode of Kelasun at the layer sizes of the 0.6B, 8B and 32B models (random weights,
+    ``--layers`` layers, default 4, attention and latent layers in turn, 8 experts of which 2 are used
+    plus a shared one, together as wide as the dense feed-forward) beside a dense Qwen3 of the same
+    sizes: tokens/s through the engine, and every kernel of the new design beside its counterpart with
+    the fraction of its roofline.  One JSON line."""
+    import torch
+
+    from tinyvllm_b200 import EngineConfig
+    from tinyvllm_b200.engine.engine import Engine
+    from tinyvllm_b200.engine.step import StepEntry
+
+    layers = args.layers if args.layers_given else 4
+    batch, prompt, steps, warmup = args.batch, PROMPT_TOKENS, min(args.steps, 64), max(args.warmup, 3)
+    peak, peak_source = peaks()
+    names = sorted({n for pair in KELASUN_LIKE for n in pair[:2] if n} | {"attention_prefill", "attention_rows"})
+    both_kinds = ("attention_tiles", "attention_tiles_singles", "attention_rows")
+    results = []
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = [size for size in KELASUN_SIZES if not args.sizes or size in args.sizes.split(",")]
+    for size in sizes:
+        row = {"size": size}
+        for label, config in (("kelasun", kelasun_config(size, layers)), ("qwen3_dense", dense_qwen3_config(size, layers))):
+            with tempfile.TemporaryDirectory() as folder:
+                Path(folder, "config.json").write_text(json.dumps(config.to_json()))
+                engine = Engine.from_config(EngineConfig(
+                    model=folder, dtype="bfloat16", weights="random", seed=0, max_model_len=CONTEXT_LIMIT,
+                    max_num_seqs=batch, max_num_batched_tokens=4096, prefill_chunk_size=2048,
+                    prefill_reserve_tokens=0, prefill_reserve_requests=0, kv_block_size=16,
+                    kv_cache_memory_bytes=2 * 1024**3, graph_batch_sizes=(batch,)))
+                decode = run_decode(engine, batch, steps, warmup, sampler, prompt_tokens=prompt)
+                prefill_ms = run_prefill(engine, repeats=5, tokens=prompt)
+                runner = engine.runner
+                rng = random.Random(5)
+                with torch.inference_mode():
+                    for r in range(batch):
+                        runner.open(f"k{r}")
+                    prompts = [StepEntry(f"k{r}", tuple(random_prompt(rng, prompt)), ()) for r in range(batch)]
+
+                    def eager_step(entries):
+                        plan = runner.plan(entries)
+                        runner.execute(runner.build_context(entries, plan))
+                        runner.manager.commit(plan)
+
+                    # the GPU is kept busy (a spin kernel) while the host queues the step's launches behind it:
+                    # the events then bracket device time, not the host's pace
+                    for entry in prompts[1:]:
+                        eager_step([entry])
+                    torch.cuda.synchronize()
+                    with KernelClock(names) as clock:
+                        torch.cuda._sleep(40_000_000)
+                        eager_step([prompts[0]])
+                    torch.cuda.synchronize()
+                    by_prompt = list(clock.marks)
+                    singles = [StepEntry(f"k{r}", (1,), (0,)) for r in range(batch)]
+                    eager_step(singles)
+                    torch.cuda.synchronize()
+                    with KernelClock(names) as clock:
+                        torch.cuda._sleep(40_000_000)
+                        eager_step(singles)
+                    torch.cuda.synchronize()
+                    by_decode = list(clock.marks)
+                    for r in range(batch):
+                        runner.close(f"k{r}")
+                kernels_out = {}
+                for phase, marks, tokens in (("prefill", by_prompt, prompt), ("decode", by_decode, batch)):
+                    found, seen = {}, {}
+                    for name, start, end in marks:
+                        kind = "dense"
+                        if label == "kelasun":
+                            # the two kinds of layers call the attention kernels in turn, the attention layer first
+                            index = seen.get(name, 0)
+                            seen[name] = index + 1
+                            kind = ("attention", "latent")[index % 2] if name in both_kinds else \
+                                "latent" if name in ("latent_prepare", "rotate_heads", "head_product") else "attention"
+                        key = name if kind == "dense" or name not in both_kinds else f"{name}[{kind}]"
+                        calls, ms, _ = found.get(key, (0, 0.0, kind))
+                        found[key] = (calls + 1, ms + start.elapsed_time(end), kind)
+                    for key, (calls, ms, kind) in sorted(found.items()):
+                        per_call = 1e3 * ms / max(1, calls)
+                        ideal, bound = kelasun_roofline(key.split("[")[0], kind, size, tokens, prompt, peak)
+                        kernels_out[f"{phase}:{key}"] = {
+                            "calls": calls, "us_per_call": round(per_call, 2), "roofline_us": round(ideal, 2),
+                            "bound": bound, "frac": round(ideal / per_call, 3) if per_call > 0 else None}
+                row[label] = {
+                    "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                    "prefill_tokens_per_s": round(prompt / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                    "weight_bytes": engine.runner.model.weight_bytes(), "kernels": kernels_out}
+                engine.close()
+                del engine
+                torch.cuda.empty_cache()
+        results.append(row)
+    sampler.stop()
+    print(json.dumps({
+        "metric": "Kelasun beside a dense Qwen3 of equal layer sizes: decode tok/s at batch "
+                  f"{batch} from context {prompt:,}, prefill tok/s of {prompt:,} tokens, bf16",
+        "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic (random weights and tokens)",
+        "config": {"layers": layers, "batch": batch, "vocab": MODEL["vocab_size"],
+                   "sizes": {k: list(v) for k, v in KELASUN_SIZES.items() if k in sizes},
+                   "latents": {k: list(v) for k, v in KELASUN_LATENTS.items() if k in sizes}, "rot_dim": KELASUN_ROT,
+                   "experts": KELASUN_EXPERTS, "top": KELASUN_TOP,
+                   "timing": "CUDA events; decode replays graphs with inputs uploaded every step, for "
+                             f"{batch} requests; kernel figures: the calls of one eager step queued behind a spin kernel, "
+                             "so that each pair of events brackets device time (warm caches)"},
+        "peaks": {"hbm_gbs": peak["hbm_gbs"], "bf16_tflops": peak["bf16_tflops"], "source": peak_source},
+        "clocks": sampler.summary(), "results": results}))
+    return 0
+
+
 def arrivals_workload(args) -> int:
     """16 requests with prompts of 64 or 512 tokens and 64 new tokens that arrive 20 ms apart, at the
     0.6B sizes, through ``Engine.submit(arrival_ns=)`` and ``Engine.step``: time to first token, time
@@ -937,10 +1139,12 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals", "gumapel"), default="0.6b",
+    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals", "gumapel", "kelasun"), default="0.6b",
                         help="0.6b: the decode and prefill measurement (default); 8b, 32b: the serving "
                              "workloads of those sizes at full depth; arrivals: 16 requests 20 ms apart; "
-                             "gumapel: the Gumapel design beside a windowed Qwen3 at equal layer sizes")
+                             "gumapel: the Gumapel design beside a windowed Qwen3 at equal layer sizes; "
+                             "kelasun: the Kelasun design beside a dense Qwen3 at equal layer sizes")
+    parser.add_argument("--sizes", default="", help="kelasun: which of 0.6b,8b,32b (default: all)")
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the configuration has (both numbers are in the line)")
     parser.add_argument("--batch", type=int, default=8)
@@ -965,6 +1169,8 @@ def main() -> int:
         return arrivals_workload(args)
     if args.workload == "gumapel":
         return gumapel_workload(args)
+    if args.workload == "kelasun":
+        return kelasun_workload(args)
     if args.eager_profile:
         return eager_profile(args, warmup)
     return headline(args, warmup)

@@ -14,6 +14,8 @@
 //   head_product      out[t, h, j] = sum_k x[t, h, k] * w[h, j, k], optionally times sigmoid(gate[t, h, j]):
 //                     one small product a head (the up-projections of latent attention, folded into the
 //                     query and applied to the attended latents)
+//   heads_place       the same result computed by a batched library product [h, t, j], put into [t, h, j]
+//                     with the gate on the way (many tokens in bfloat16)
 #include "common.cuh"
 
 // ------------------------------------------------------------ projection_norm
@@ -204,6 +206,8 @@ extern "C" int tvb_rotate_heads(const void* src, long long src_token_stride, lon
 #define HP_TOKENS 8
 #define HP_WARPS 8
 
+#define HP_COLUMNS 32          // output columns a block takes (grid.z walks the rest)
+
 template <typename T>
 __global__ void head_product_kernel(const T* x, int64_t x_token_stride, int64_t x_head_stride,
                                     const T* __restrict__ w, T* out, int64_t out_token_stride,
@@ -220,7 +224,8 @@ __global__ void head_product_kernel(const T* x, int64_t x_token_stride, int64_t 
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* w_head = w + (int64_t)head * n * k;
-    for (int j = warp; j < n; j += HP_WARPS) {
+    const int last = min(n, (int)(blockIdx.z + 1) * HP_COLUMNS);
+    for (int j = blockIdx.z * HP_COLUMNS + warp; j < last; j += HP_WARPS) {
         const T* w_row = w_head + (int64_t)j * k;
         float sums[HP_TOKENS];
 #pragma unroll
@@ -256,7 +261,8 @@ extern "C" int tvb_head_product(const void* x, long long x_token_stride, long lo
     const size_t smem = (size_t)HP_TOKENS * k * sizeof(float);
     if (smem > 48 * 1024) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((tokens + HP_TOKENS - 1) / HP_TOKENS, heads);
+    dim3 grid((tokens + HP_TOKENS - 1) / HP_TOKENS, heads, (n + HP_COLUMNS - 1) / HP_COLUMNS);
+    if (grid.z > 65535) return TVB_BAD_ARGUMENT;
 #define GO(T) head_product_kernel<T><<<grid, HP_WARPS * 32, smem, s>>>(                                          \
         (const T*)x, x_token_stride, x_head_stride, (const T*)w, (T*)out, out_token_stride, out_head_stride,     \
         (const T*)gate, gate_token_stride, tokens, n, k)
@@ -264,5 +270,44 @@ extern "C" int tvb_head_product(const void* x, long long x_token_stride, long lo
     else if (dtype == TVB_BF16) GO(bf16);
     else return TVB_BAD_ARGUMENT;
 #undef GO
+    return tvb_last_error();
+}
+
+// ---------------------------------------------------------------- heads_place
+// dst[t, h, j] = src[h, t, j] (times sigmoid(gate[t, h * n + j])): the result of a batched library product,
+// one batch a head, put where the next step reads it, with the gate on the way.
+template <typename T>
+__global__ void heads_place_kernel(const T* __restrict__ src, T* dst, int64_t dst_token_stride,
+                                   int64_t dst_head_stride, const T* gate, int64_t gate_token_stride, int tokens,
+                                   int heads, int n) {
+    const int64_t index = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= (int64_t)tokens * heads * n) return;
+    const int j = (int)(index % n);
+    const int head = (int)((index / n) % heads);
+    const int64_t token = index / ((int64_t)n * heads);
+    float v = to_float<T>(src[((int64_t)head * tokens + token) * n + j]);
+    if (gate) {
+        const float g = to_float<T>(gate[token * gate_token_stride + (int64_t)head * n + j]);
+        v = __fmul_rn(v, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g))));
+    }
+    dst[token * dst_token_stride + head * dst_head_stride + j] = from_float<T>(v);
+}
+
+extern "C" int tvb_heads_place(const void* src, void* dst, long long dst_token_stride, long long dst_head_stride,
+                               const void* gate, long long gate_token_stride, int tokens, int heads, int n, int dtype,
+                               void* stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || n <= 0) return TVB_BAD_ARGUMENT;
+    const int64_t count = (int64_t)tokens * heads * n;
+    const int64_t blocks = (count + 255) / 256;
+    if (blocks > 2147483647LL) return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == TVB_F32)
+        heads_place_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)src, (float*)dst, dst_token_stride,
+                                                                  dst_head_stride, (const float*)gate, gate_token_stride, tokens, heads, n);
+    else if (dtype == TVB_BF16)
+        heads_place_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)src, (bf16*)dst, dst_token_stride,
+                                                                 dst_head_stride, (const bf16*)gate, gate_token_stride, tokens, heads, n);
+    else return TVB_BAD_ARGUMENT;
     return tvb_last_error();
 }

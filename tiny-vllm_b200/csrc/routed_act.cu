@@ -58,12 +58,15 @@ __global__ void route_act_kernel(const float* __restrict__ logits, int64_t logit
         for (int e = lane; e < experts; e += 32) share[e] = __fdiv_rn(share[e], sum);
     }
     __syncthreads();
-    if (weights_out)
+    if (weights_out && blockIdx.y == 0)
         for (int e = threadIdx.x; e < experts; e += blockDim.x) weights_out[token * experts + e] = share[e];
     const T* src = up + token * up_stride;
     T* dst = out + token * out_stride;
     const int routed = experts * ff;
-    for (int c = threadIdx.x; c < routed + shared_ff; c += blockDim.x) {
+    // grid.y shares the columns: every block finds the token's experts for itself (a few dozen logits)
+    const int per_block = (routed + shared_ff + gridDim.y - 1) / gridDim.y;
+    const int begin = blockIdx.y * per_block, end = min(routed + shared_ff, begin + per_block);
+    for (int c = begin + threadIdx.x; c < end; c += blockDim.x) {
         const float a = expert_act<ACT>(to_float<T>(src[c]));
         dst[c] = from_float<T>(c < routed ? __fmul_rn(a, share[c / ff]) : a);
     }
@@ -80,8 +83,14 @@ extern "C" int tvb_route_act(const float* logits, long long logits_stride, const
         return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const long long columns = (long long)experts * ff + shared_ff;
-    const int threads = columns >= 4096 ? 512 : 256;
-#define GO(T, ACT) route_act_kernel<T, ACT><<<tokens, threads, 0, s>>>(                                      \
+    const int threads = 256;
+    // few tokens: the columns of a token are spread over several blocks, so that the GPU has some 300 of them
+    long long split = tokens >= 296 ? 1 : (296 + tokens - 1) / tokens;
+    const long long most = (columns + 4 * threads - 1) / (4 * threads);
+    if (split > most) split = most;
+    if (split > 65535) split = 65535;
+    const dim3 grid(tokens, (unsigned)split);
+#define GO(T, ACT) route_act_kernel<T, ACT><<<grid, threads, 0, s>>>(                                      \
         logits, logits_stride, (const T*)up, up_stride, (T*)out, out_stride, weights_out, experts, top, ff, shared_ff)
     if (dtype == TVB_F32 && act == TVB_ACT_RELU2) GO(float, TVB_ACT_RELU2);
     else if (dtype == TVB_F32) GO(float, TVB_ACT_SILU_PLAIN);

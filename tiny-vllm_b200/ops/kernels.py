@@ -596,6 +596,7 @@ def rotate_heads(src: torch.Tensor, dst: torch.Tensor, inv_freq: torch.Tensor, m
 
 
 HEAD_PRODUCT_MAX_K = 1536        # eight float32 rows of x wait in 48 KB of shared memory
+HEAD_PRODUCT_LIBRARY_TOKENS = 64   # bfloat16 tokens from which the products go to the batched library product
 
 
 def head_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, gate: torch.Tensor | None = None) -> None:
@@ -613,6 +614,16 @@ def head_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, gate: t
         raise KernelError(f"head_product: one dtype, equal token counts, k up to {HEAD_PRODUCT_MAX_K}")
     if gate is not None and (gate.shape != (tokens, heads * n) or gate.stride(1) != 1 or gate.dtype != x.dtype):
         raise KernelError("head_product: gate must be [tokens, heads * n] of the same dtype with contiguous rows")
+    if x.dtype == torch.bfloat16 and tokens >= HEAD_PRODUCT_LIBRARY_TOKENS:
+        # many tokens: one batched library product (a batch a head) on the tensor cores, then the result goes
+        # to its place, with the gate on the way
+        by_head = torch.bmm(x.transpose(0, 1), w.transpose(1, 2))            # [heads, tokens, n]
+        fn = _fn("latent_prepare", "tvb_heads_place",
+                 [c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                  c_void_p])
+        _check(fn(by_head.data_ptr(), out.data_ptr(), *o_strides, _ptr(gate), 0 if gate is None else gate.stride(0),
+                  tokens, heads, n, dtype_tag(x.dtype), _stream()), "heads_place")
+        return
     fn = _fn("latent_prepare", "tvb_head_product",
              [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong,
               c_int, c_int, c_int, c_int, c_int, c_void_p])
