@@ -53,9 +53,16 @@ KELASUN_CONFIGS = {
         _l(2, 32, 64, 32, 64, 256, 250000.0, (4.0, 128.0, 32.0, 1.0), KelasunExperts(16, 4, 16, 16)),
         _a(8, 8, 32, 16, (0.7, 64), KelasunExperts(16, 4, 16, 16)),
         _l(2, 32, 0, 32, 64, 96, None, None, None))),
+    # sizes that fit no vector access at all: a width and a vocabulary that are no multiples of four, odd head
+    # sizes, a single head, two experts of which one is used, a shared expert of three columns
+    "d": KelasunConfig(vocab=101, width=50, norm_eps=1e-5, postln_alpha=2.0, logit_scale=1.5, layers=(
+        _a(2, 1, 7, 10, (0.2, 3), KelasunExperts(2, 1, 5, 3)),
+        _l(1, 5, 2, 7, 9, 11, 100.0, (2.0, 16.0, 4.0, 1.0), KelasunExperts(2, 2, 6, 0)),
+        _l(3, 5, 6, 3, 9, 11, 100.0, None, None),
+        _a(1, 1, 7, 10, None, None))),
 }
-KELASUN_SEEDS = {"a": 21, "b": 22, "c": 23}
-KELASUN_PAGES = {"a": 16, "b": 8, "c": 16}
+KELASUN_SEEDS = {"a": 21, "b": 22, "c": 23, "d": 24}
+KELASUN_PAGES = {"a": 16, "b": 8, "c": 16, "d": 4}
 
 
 def tensors_of(config: KelasunConfig, seed: int) -> dict:

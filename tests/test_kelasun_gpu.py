@@ -90,6 +90,25 @@ def test_norm_over_whole_projections_and_query_temperature(dtype):
                             torch.tensor(positions, dtype=torch.int32, device=CUDA), 1e-5, temperature=(coef, every))
     close(dev, want, dtype)
     assert torch.equal(dev[:, q_cols + k_cols:].cpu(), proj[:, q_cols + k_cols:])          # the rest is untouched
+    # the same launch may store: the second segment as 2 kv heads of 9 keys, and 2 x 3 values from the rest
+    page, pages = 4, 4
+    key_cache = torch.full((pages, 2, page, 9), float("nan"), dtype=dtype, device=CUDA)
+    value_cache = torch.full((pages, 2, page, 3), float("nan"), dtype=dtype, device=CUDA)
+    slots = [5, 0, 15, 9, -1, 2]
+    again = proj.to(CUDA)
+    kernels.projection_norm(again, [(0, q_cols, qw.to(CUDA), True), (q_cols, k_cols, kw.to(CUDA), False)],
+                            torch.tensor(positions, dtype=torch.int32, device=CUDA), 1e-5, temperature=(coef, every),
+                            store=dict(slots=torch.tensor(slots, dtype=torch.int32, device=CUDA), key_cache=key_cache,
+                                       value_cache=value_cache, v_at=q_cols + k_cols))
+    assert torch.equal(again, dev)
+    for t, slot in enumerate(slots):
+        if slot < 0:
+            continue
+        for head in range(2):
+            assert torch.equal(key_cache[slot // page, head, slot % page], dev[t, q_cols + 9 * head:q_cols + 9 * head + 9])
+            assert torch.equal(value_cache[slot // page, head, slot % page],
+                               proj[t, q_cols + k_cols + 3 * head:q_cols + k_cols + 3 * head + 3].to(CUDA))
+    assert torch.isnan(key_cache.float()).sum().item() == (pages * page - 5) * 2 * 9      # no other row was touched
     # positions 8 and 9 lie on the two sides of a period's edge: (p + 1) / every is 0 and then 1
     ratio = (dev[2, :q_cols].double() / want[2, :q_cols].cuda()).mean().item()
     assert ratio == pytest.approx(1.0, abs=2e-2)

@@ -5,7 +5,8 @@
 //   projection_norm   in place on segments of a packed projection row: v * rsqrt(mean(v^2) + eps) * w
 //                     over the whole segment (all heads at once, weight of the segment's size), and,
 //                     for segments that ask for it, times the query temperature
-//                     1 + coef * ln(floor((p + 1) / every) + 1) of the token's position p
+//                     1 + coef * ln(floor((p + 1) / every) + 1) of the token's position p; optionally the
+//                     second segment (keys) and the values behind it go to the token's cache rows as well
 //   latent_prepare    from a packed projection row [.. dq .. | .. dkv ..]: the query latent
 //                     RMSnorm(dq) * w_q to a buffer; the key/value latent RMSnorm(dkv[:rank]) * w_kv and
 //                     the rotated rest of dkv side by side, [latent | rotated], to the token's cache slot
@@ -25,9 +26,19 @@ struct NormSegment {
     int tempered;
 };
 
+// Where the second segment (the keys) and the values behind it go once they are ready: the token's rows
+// of the paged caches [pages, num_kv, page, key_dim / value_dim].  `slots` null: nothing is stored.
+struct CacheRows {
+    const int* slots;
+    void* key_cache;
+    void* value_cache;
+    int num_kv, key_dim, value_dim, page_size, v_at;
+};
+
 template <typename T, typename W>
 __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment first, NormSegment second,
-                                       const int* __restrict__ positions, float eps, float coef, int every) {
+                                       const int* __restrict__ positions, float eps, float coef, int every,
+                                       CacheRows rows) {
     __shared__ float scratch[32];
     const NormSegment seg = blockIdx.y == 0 ? first : second;
     T* row = proj + (int64_t)blockIdx.x * stride + seg.at;
@@ -44,23 +55,46 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
         const int p = max(positions[blockIdx.x], 0);
         temperature = __fmaf_rn(coef, logf((float)((p + 1) / every + 1)), 1.0f);
     }
+    // the block of the second segment also stores: the normalised keys and the values to the token's cache rows
+    const int slot = (blockIdx.y == 1 && rows.slots) ? rows.slots[blockIdx.x] : -1;
+    const int64_t page_row = slot >= 0 ? (int64_t)(slot / rows.page_size) * rows.num_kv : 0;
+    const int offset = slot >= 0 ? slot % rows.page_size : 0;
     for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
         float o = __fmul_rn(__fmul_rn(to_float<T>(row[i]), inverse), to_float<W>(weight[i]));
         if (seg.tempered) o = __fmul_rn(o, temperature);
-        row[i] = from_float<T>(o);
+        const T rounded = from_float<T>(o);
+        row[i] = rounded;
+        if (slot >= 0) {
+            const int head = i / rows.key_dim, dim = i % rows.key_dim;
+            ((T*)rows.key_cache)[((page_row + head) * rows.page_size + offset) * rows.key_dim + dim] = rounded;
+        }
+    }
+    if (slot >= 0) {
+        const T* values = proj + (int64_t)blockIdx.x * stride + rows.v_at;
+        for (int i = threadIdx.x; i < rows.num_kv * rows.value_dim; i += blockDim.x) {
+            const int head = i / rows.value_dim, dim = i % rows.value_dim;
+            ((T*)rows.value_cache)[((page_row + head) * rows.page_size + offset) * rows.value_dim + dim] = values[i];
+        }
     }
 }
 
-// Two segments a launch (queries and keys); `second_cols` = 0 leaves the second out.
-extern "C" int tvb_projection_norm(void* proj, long long stride, int first_at, int first_cols,
-                                   const void* first_weight, int first_tempered, int second_at, int second_cols,
-                                   const void* second_weight, int second_tempered, int weight_dtype,
-                                   const int* positions, float eps, float coef, int every, int tokens, int dtype,
-                                   void* stream) {
+// Two segments a launch (queries and keys); `second_cols` = 0 leaves the second out.  With `slots` the second
+// segment is num_kv keys of key_dim elements: they go, normalised, to `key_cache`, and the num_kv values of
+// value_dim elements from column `v_at` on go to `value_cache`, both at the token's slot (negative: nowhere).
+extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first_at, int first_cols,
+                                         const void* first_weight, int first_tempered, int second_at, int second_cols,
+                                         const void* second_weight, int second_tempered, int weight_dtype,
+                                         const int* positions, float eps, float coef, int every, const int* slots,
+                                         void* key_cache, void* value_cache, int num_kv, int key_dim, int value_dim,
+                                         int page_size, int v_at, int tokens, int dtype, void* stream) {
     if (tokens <= 0) return 0;
     if (first_cols <= 0 || second_cols < 0 || !first_weight || (second_cols > 0 && !second_weight) ||
         ((first_tempered || second_tempered) && every > 0 && !positions))
         return TVB_BAD_ARGUMENT;
+    if (slots && (!key_cache || !value_cache || num_kv <= 0 || key_dim <= 0 || value_dim <= 0 || page_size <= 0 ||
+                  v_at < 0 || second_cols != num_kv * key_dim))
+        return TVB_BAD_ARGUMENT;
+    const CacheRows rows{slots, key_cache, value_cache, num_kv, key_dim, value_dim, page_size, v_at};
     cudaStream_t s = (cudaStream_t)stream;
     NormSegment first{first_at, first_cols, first_weight, first_tempered};
     NormSegment second{second_at, second_cols, second_weight, second_tempered};
@@ -70,8 +104,10 @@ extern "C" int tvb_projection_norm(void* proj, long long stride, int first_at, i
         const int count = tokens - start < 65535 ? tokens - start : 65535;
         dim3 grid(count, second_cols > 0 ? 2 : 1);
         const int* p = positions ? positions + start : nullptr;
+        CacheRows part = rows;
+        if (part.slots) part.slots += start;
 #define GO(T, W) projection_norm_kernel<T, W><<<grid, threads, 0, s>>>((T*)proj + (int64_t)start * stride, stride, \
-                                                                        first, second, p, eps, coef, every)
+                                                                        first, second, p, eps, coef, every, part)
         if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float);
         else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) GO(bf16, bf16);
         else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float);
@@ -79,6 +115,16 @@ extern "C" int tvb_projection_norm(void* proj, long long stride, int first_at, i
 #undef GO
     }
     return tvb_last_error();
+}
+
+extern "C" int tvb_projection_norm(void* proj, long long stride, int first_at, int first_cols,
+                                   const void* first_weight, int first_tempered, int second_at, int second_cols,
+                                   const void* second_weight, int second_tempered, int weight_dtype,
+                                   const int* positions, float eps, float coef, int every, int tokens, int dtype,
+                                   void* stream) {
+    return tvb_projection_norm_store(proj, stride, first_at, first_cols, first_weight, first_tempered, second_at,
+                                     second_cols, second_weight, second_tempered, weight_dtype, positions, eps, coef,
+                                     every, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, tokens, dtype, stream);
 }
 
 // ------------------------------------------------------------- latent_prepare

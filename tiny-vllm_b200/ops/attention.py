@@ -286,23 +286,29 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
         raise kernels.KernelError("the kernel that prepares q and k here turns pairs without a factor on cosine "
                                   "and sine; a scaled rotation needs the mixer that applies it")
     head_norm = mixer.qk_norm
+    prepared = False
     if head_norm == "whole":
         # the norm over all heads at once (and the query temperature) first, in place; the preparing kernel
         # then only stores k and v
+        plain_rest = position is None and mixer.value_mix is None
         kernels.projection_norm(
             projected, [(q_at, mixer.q_cols, mixer.q_norm_weight, mixer.query_temperature is not None),
                         (k_at, mixer.k_cols, mixer.k_norm_weight, False)],
-            ctx.positions, mixer.qk_norm_eps, temperature=mixer.query_temperature)
+            ctx.positions, mixer.qk_norm_eps, temperature=mixer.query_temperature,
+            store=dict(slots=ctx.slots[group], key_cache=keys, value_cache=values, v_at=v_at)
+            if plain_rest and writes else None)
         head_norm = None
-    kernels.qkv_prepare(
-        projected, q_at=q_at, k_at=k_at, v_at=v_at, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads,
-        key_dim=mixer.key_dim, value_dim=mixer.value_dim, positions=ctx.positions, norm=head_norm,
-        q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps,
-        inv_freq=None if position is None else position.inv_freq,
-        rot_dims=0 if position is None else position.rot_dims,
-        pairing="interleaved" if position is None else position.pairing,
-        slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values,
-        v_first=v_first, blend=mixer.vmix if v_first is not None else None)
+        prepared = plain_rest           # nothing is left to rotate or blend: the norm kernel stored k and v itself
+    if not prepared:
+        kernels.qkv_prepare(
+            projected, q_at=q_at, k_at=k_at, v_at=v_at, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads,
+            key_dim=mixer.key_dim, value_dim=mixer.value_dim, positions=ctx.positions, norm=head_norm,
+            q_weight=mixer.q_norm_weight, k_weight=mixer.k_norm_weight, eps=mixer.qk_norm_eps,
+            inv_freq=None if position is None else position.inv_freq,
+            rot_dims=0 if position is None else position.rot_dims,
+            pairing="interleaved" if position is None else position.pairing,
+            slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values,
+            v_first=v_first, blend=mixer.vmix if v_first is not None else None)
     gate = projected[:, g_at:g_at + mixer.gate_cols] if mixer.gate else None
     queries = projected[:, q_at:q_at + mixer.q_cols]
     heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, key_dim=mixer.key_dim,

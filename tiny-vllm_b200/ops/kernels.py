@@ -504,11 +504,14 @@ def scale_float32(x: torch.Tensor, factor: float) -> torch.Tensor:
 
 # ------------------------------------------- norms over whole projections, latents, head products
 def projection_norm(proj: torch.Tensor, segments, positions: torch.Tensor | None, eps: float, *,
-                    temperature: tuple[float, int] | None = None) -> None:
+                    temperature: tuple[float, int] | None = None, store: dict | None = None) -> None:
     """In place on a packed projection [tokens, columns]: every segment (first column, columns, weight
     [columns], tempered) becomes v * rsqrt(mean(v^2) + eps) * weight over the whole segment; a tempered
     segment is also multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) of the token's position p
-    (``temperature`` = (coef, every)).  One or two segments."""
+    (``temperature`` = (coef, every)).  One or two segments.  ``store`` (slots int32 [tokens], key_cache
+    [pages, num_kv, page, key_dim], value_cache [pages, num_kv, page, value_dim], v_at): the second segment
+    is the token's keys, which go, normalised, to its cache rows, together with the values from column
+    ``v_at`` on."""
     _need_cuda(proj, positions, *[seg[2] for seg in segments])
     if proj.dim() != 2 or proj.stride(1) != 1 or not 1 <= len(segments) <= 2:
         raise KernelError("projection_norm wants [tokens, columns] with contiguous rows and one or two segments")
@@ -523,12 +526,29 @@ def projection_norm(proj: torch.Tensor, segments, positions: torch.Tensor | None
         raise KernelError("projection_norm: a temperature needs int32 positions [tokens]")
     first = segments[0]
     second = segments[1] if len(segments) > 1 else (0, 0, None, False)
-    fn = _fn("latent_prepare", "tvb_projection_norm",
+    slots = key_cache = value_cache = None
+    num_kv = key_dim = value_dim = page_size = v_at = 0
+    if store is not None:
+        slots, key_cache, value_cache, v_at = store["slots"], store["key_cache"], store["value_cache"], store["v_at"]
+        _need_cuda(slots, key_cache, value_cache)
+        if len(segments) != 2 or key_cache.dim() != 4 or value_cache.dim() != 4 or \
+                key_cache.shape[:3] != value_cache.shape[:3] or not key_cache.is_contiguous() or \
+                not value_cache.is_contiguous() or key_cache.dtype != proj.dtype or value_cache.dtype != proj.dtype or \
+                slots.dtype != torch.int32 or slots.shape != (tokens,):
+            raise KernelError("projection_norm: storing needs two segments, int32 slots [tokens] and contiguous caches "
+                              "[pages, num_kv, page_size, key / value size] of the projection's dtype")
+        _, num_kv, page_size, key_dim = key_cache.shape
+        value_dim = value_cache.shape[3]
+        if second[1] != num_kv * key_dim or v_at < 0 or v_at + num_kv * value_dim > proj.shape[1]:
+            raise KernelError("projection_norm: the second segment is the keys of all kv heads, the values lie inside the row")
+    fn = _fn("latent_prepare", "tvb_projection_norm_store",
              [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-              c_float, c_float, c_int, c_int, c_int, c_void_p])
+              c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_void_p])
     _check(fn(proj.data_ptr(), proj.stride(0), first[0], first[1], first[2].data_ptr(), int(bool(first[3])),
               second[0], second[1], _ptr(second[2]), int(bool(second[3])), dtype_tag(first[2].dtype),
-              _ptr(positions), eps, float(coef), int(every), tokens, dtype_tag(proj.dtype), _stream()),
+              _ptr(positions), eps, float(coef), int(every), _ptr(slots), _ptr(key_cache), _ptr(value_cache), num_kv,
+              key_dim, value_dim, page_size, v_at, tokens, dtype_tag(proj.dtype), _stream()),
            "projection_norm")
 
 
