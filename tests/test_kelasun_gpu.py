@@ -402,7 +402,7 @@ def test_every_way_of_cutting_gives_the_plain_logits(cut, name, dtype, folders):
     steps = {"whole": lambda: rh.whole(requests), "tail": lambda: rh.tail_by_one(requests, 40),
              "portions": lambda: rh.portions(requests, 3, sizes=(2, 3, 5, 8, 13, 31, 64, 100, 200)),
              "mixed": lambda: rh.mixed(requests, 4, live=4, decode_tail=20, sizes=(2, 3, 7, 16, 40, 90))}[cut]()
-    pages = -(-rh.live_token_need(steps, page) // page) if cut == "mixed" else 64
+    pages = -(-rh.live_token_need(steps, page) // page) if cut == "mixed" else max(64, -(-448 // page))
     runner = make_runner(folders[name], dtype, page, pages)
     with torch.inference_mode():
         got = rh.run_steps(runner, steps)
