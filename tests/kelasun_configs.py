@@ -65,8 +65,9 @@ KELASUN_SEEDS = {"a": 21, "b": 22, "c": 23, "d": 24}
 KELASUN_PAGES = {"a": 16, "b": 8, "c": 16, "d": 4}
 
 
-def tensors_of(config: KelasunConfig, seed: int) -> dict:
-    """Checkpoint tensors (float32) of ``config``, drawn from ``seed``."""
+def tensors_of(config: KelasunConfig, seed: int, second_norms: bool = False) -> dict:
+    """Checkpoint tensors (float32) of ``config``, drawn from ``seed``.  ``second_norms``: layers without a
+    feed-forward hold a second norm all the same."""
     g = torch.Generator().manual_seed(seed)
 
     def matrix(rows, cols, gain=1.0):
@@ -110,17 +111,20 @@ def tensors_of(config: KelasunConfig, seed: int) -> dict:
             if m.shared_ff:
                 t[p + "mlp.shared.up"] = matrix(m.shared_ff, d, 1.5)
                 t[p + "mlp.shared.down"] = matrix(d, m.shared_ff)
+        elif second_norms:
+            t[p + "norm2"] = around_one(d)
     return t
 
 
-def write_folder(folder, config: KelasunConfig, seed: int, dtype=torch.float32):
+def write_folder(folder, config: KelasunConfig, seed: int, dtype=torch.float32, second_norms: bool = False):
     """config.json and model.safetensors of ``config`` in ``folder``.  The values are rounded to
     bfloat16 whatever ``dtype`` stores them as, so that both number formats run the same model."""
     from safetensors.torch import save_file
 
     folder.mkdir(parents=True, exist_ok=True)
     (folder / "config.json").write_text(json.dumps(config.to_json(), indent=1), encoding="utf-8")
-    tensors = {name: value.to(torch.bfloat16).to(dtype).contiguous() for name, value in tensors_of(config, seed).items()}
+    tensors = {name: value.to(torch.bfloat16).to(dtype).contiguous()
+               for name, value in tensors_of(config, seed, second_norms).items()}
     save_file(tensors, str(folder / "model.safetensors"))
     return folder
 

@@ -163,6 +163,8 @@ def forward(config, weights, tokens, *, streams=None):
         if layer.get("mlp") is not None:
             x = layer_norm(alpha * x + routed_experts(x, w, f"l{index}.mlp", layer["mlp"]),
                            w[f"l{index}.norm2"], eps)
+        elif f"l{index}.norm2" in w:          # a second norm without a feed-forward: nothing is added
+            x = layer_norm(alpha * x, w[f"l{index}.norm2"], eps)
         if streams is not None:
             streams.append(x.clone())
     x = layer_norm(x, w["final.norm"], eps)

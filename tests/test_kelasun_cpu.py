@@ -46,13 +46,33 @@ def test_config_refusals():
 def test_the_model_declares_exactly_the_checkpoint_tensors(name):
     config = KELASUN_CONFIGS[name]
     model = Model(config.to_spec(), device="cpu", dtype=torch.float32)
-    declared = {}
+    declared, may_lack = {}, set()
     for _, spec in model.param_targets():
         for source in spec.sources:
             declared[source.name] = declared.get(source.name, 0) + 1
+            if spec.optional:
+                may_lack.add(source.name)
     tensors = tensors_of(config, KELASUN_SEEDS[name])
-    assert set(declared) == set(tensors)
+    assert set(declared) - may_lack == set(tensors)
     assert all(count == 1 for count in declared.values())
+    # a layer without a feed-forward may hold a second norm all the same, and only such a layer
+    assert may_lack == {f"l{i}.norm2" for i, layer in enumerate(config.layers) if layer.mlp is None}
+    assert set(declared) == set(tensors_of(config, KELASUN_SEEDS[name], second_norms=True))
+
+
+def test_a_tensor_a_part_declares_optional_may_be_absent():
+    from tinyvllm_b200.parts.base import ParamSpec, Part
+    from tinyvllm_b200.weights.loader import WeightsError, bind_tensors
+
+    part = Part()
+    targets = [(part, ParamSpec.single("a", "x.a", (3,), role="vector")),
+               (part, ParamSpec.single("b", "x.b", (2,), role="vector", optional=True))]
+    bind_tensors(targets, {"x.a": torch.ones(3)}, dtype=torch.float32, device="cpu")
+    assert part.b is None and part.a.shape == (3,)
+    bind_tensors(targets, {"x.a": torch.ones(3), "x.b": torch.zeros(2)}, dtype=torch.float32, device="cpu")
+    assert part.b.shape == (2,)
+    with pytest.raises(WeightsError):
+        bind_tensors(targets, {"x.b": torch.zeros(2)}, dtype=torch.float32, device="cpu")
 
 
 def test_cache_groups_hold_latents_once():

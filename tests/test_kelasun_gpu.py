@@ -431,6 +431,20 @@ def test_a_request_is_not_moved_by_its_neighbours(dtype, folders):
         assert errors[len(errors) * 39 // 40 - 1] <= 2e-2
 
 
+def test_a_second_norm_without_a_feed_forward(tmp_path):
+    """A checkpoint that holds the second norm of a layer without a feed-forward: the layer then ends with
+    x <- norm2(alpha x)."""
+    name = "a"
+    folder = write_folder(tmp_path / "with_norms", KELASUN_CONFIGS[name], KELASUN_SEEDS[name], second_norms=True)
+    requests = {"n": tokens_of(KELASUN_CONFIGS[name].vocab, 90, 77)}
+    runner = make_runner(folder, torch.float32, 16, 16)
+    with torch.inference_mode():
+        got = rh.run_steps(runner, rh.portions(requests, 5, sizes=(2, 9, 40)))
+    compare(got, folder, requests, torch.float32)
+    plain_logits = oracle_logits(write_folder(tmp_path / "without", KELASUN_CONFIGS[name], KELASUN_SEEDS[name]), requests)["n"]
+    assert (plain_logits - oracle_logits(folder, requests)["n"]).abs().max() > 1e-3          # the norm matters
+
+
 def test_long_decoding(folders):
     """A prompt of five tokens and 330 tokens decoded one by one, float32, past a chunk border of the
     keys and several periods of the query temperature."""

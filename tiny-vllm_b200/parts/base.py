@@ -82,11 +82,12 @@ class ParamSpec:
     sources: tuple[ParamSource, ...]
     role: str = "matrix"
     init: str = "normal"
+    optional: bool = False        # a checkpoint may lack it: the part is then bound None (random weights draw none)
 
     @staticmethod
     def single(attr: str, name: str, shape: tuple[int, ...], *, role: str = "matrix",
-               init: str = "normal") -> "ParamSpec":
-        return ParamSpec(attr, shape, (ParamSource(name, 0, shape[0]),), role, init)
+               init: str = "normal", optional: bool = False) -> "ParamSpec":
+        return ParamSpec(attr, shape, (ParamSource(name, 0, shape[0]),), role, init, optional)
 
     @staticmethod
     def scalar(attr: str, name: str, *, init: str = "unit_interval") -> "ParamSpec":

@@ -117,8 +117,8 @@ class ParallelResidualBlock(Block):
 
 class PostNormResidualBlock(Block):
     """Norm after the sum: x <- norm1(alpha * x + mixer(x)), then x <- norm2(alpha * x +
-    feed_forward(x)); both sublayers read x itself.  A layer may have no feed-forward (and then no
-    second norm).  The stream x is float32 whatever the storage type; the norms hand on, beside it,
+    feed_forward(x)); both sublayers read x itself.  A layer may have no feed-forward: it then has no
+    second step, unless its checkpoint holds the second norm, which is then applied to alpha * x.  The stream x is float32 whatever the storage type; the norms hand on, beside it,
     its one rounding to the storage type (``stream.rounded``), which is what the next products read.
     The block returns (None, stream): nothing is left to add."""
 
@@ -128,10 +128,13 @@ class PostNormResidualBlock(Block):
         # the norms' weights are stored under the norms' own names, "<layer>.<norm name>"
         self.mixer_norm = ctx.build("norm", norm.with_params(name=f"{ctx.prefix}.{mixer_norm_name}"), ctx)
         self.mixer = ctx.build("mixer", mixer, ctx.child(mixer_name))
-        self.feed_forward = self.feed_forward_norm = None
+        self.feed_forward = None
+        # a layer without a feed-forward has no second step; if its checkpoint holds the second norm all the
+        # same, the step is x <- norm2(alpha x), the formula with nothing added
+        self.feed_forward_norm = ctx.build(
+            "norm", norm.with_params(name=f"{ctx.prefix}.{feed_forward_norm_name}",
+                                     **({"optional": True} if feed_forward is None else {})), ctx)
         if feed_forward is not None:
-            self.feed_forward_norm = ctx.build(
-                "norm", norm.with_params(name=f"{ctx.prefix}.{feed_forward_norm_name}"), ctx)
             self.feed_forward = ctx.build("feed_forward", feed_forward, ctx.child(feed_forward_name))
         for part in (self.mixer_norm, self.feed_forward_norm):
             if part is not None and not hasattr(part, "post"):
@@ -154,6 +157,8 @@ class PostNormResidualBlock(Block):
         x, stream = self.mixer_norm.post(stream, self.mixer.forward(x, ctx, run), self.alpha)
         if self.feed_forward is not None:
             x, stream = self.feed_forward_norm.post(stream, self.feed_forward.forward(x, ctx), self.alpha)
+        elif self.feed_forward_norm.weight is not None:
+            x, stream = self.feed_forward_norm.post(stream, None, self.alpha)
         if x is not stream:
             stream.rounded = x
         return None, stream

@@ -83,15 +83,18 @@ class StreamLayerNorm(Part):
     in float32.  ``post`` returns (out rounded once to the storage type, out in float32): the first
     feeds the next products, the second is the stream.  In the float32 path both are one tensor."""
 
-    def __init__(self, ctx: BuildContext, *, width: int, eps: float, name: str | None = None) -> None:
+    def __init__(self, ctx: BuildContext, *, width: int, eps: float, name: str | None = None,
+                 optional: bool = False) -> None:
         self.width = width
         self.eps = float(eps)
         self.name = name if name is not None else f"{ctx.prefix}.weight"
         self.out_dtype = ctx.dtype
+        self.optional = optional          # the checkpoint may lack the weight: ``weight`` stays None
         self.weight = None
 
     def param_specs(self):
-        return [ParamSpec.single("weight", self.name, (self.width,), role="vector", init="around_one")]
+        return [ParamSpec.single("weight", self.name, (self.width,), role="vector", init="around_one",
+                                 optional=self.optional)]
 
     def post(self, x, y, alpha: float = 1.0):
         """(LN(alpha * x + y) in the storage type, the same in float32); y may be None."""

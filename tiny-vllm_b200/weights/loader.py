@@ -129,11 +129,16 @@ def bind_tensors(targets, named_tensors, *, dtype, device, folder="<memory>",
         if source.cols is not None:
             rows = rows[:, source.col_start:source.col_start + source.cols]
         rows.copy_(tensor.reshape(rows.shape))
-    missing = sorted(name for name in routes if name not in seen)
+    # a tensor its part declares optional may be absent as a whole (all its sources); the part is bound None
+    absent = {(id(part), spec.attr) for part, spec in targets
+              if spec.optional and not any(source.name in seen for source in spec.sources)}
+    missing = sorted(name for name, (part, spec, _) in routes.items()
+                     if name not in seen and (id(part), spec.attr) not in absent)
     if missing or unexpected or wrong:
         raise WeightsError(folder, missing, sorted(unexpected), wrong)
     for part, spec in targets:
-        part.bind(spec.attr, destinations[(id(part), spec.attr)])
+        key = (id(part), spec.attr)
+        part.bind(spec.attr, None if key in absent else destinations[key])
 
 
 def load_checkpoint(targets, folder, *, dtype, device, optional=(), aliases=None) -> None:

@@ -29,6 +29,8 @@ def random_tensors(targets, seed: int, device="cpu") -> Iterator[tuple[str, torc
     generator = torch.Generator(device=device)
     generator.manual_seed(seed)
     for _part, spec in targets:
+        if spec.optional:
+            continue
         for source in spec.sources:
             shape = source_shape(spec, source)
             if spec.role == "integer":
