@@ -906,13 +906,18 @@ KELASUN_LIKE = (
 )
 
 
+def kelasun_expert_width(ff: int) -> int:
+    """A third of the dense feed-forward width, rounded down to a multiple of 64."""
+    return ff // (KELASUN_TOP + 1) // 64 * 64
+
+
 def kelasun_config(size: str, layers: int):
     from tinyvllm_b200.models import KelasunConfig
     from tinyvllm_b200.models.kelasun import KelasunExperts, KelasunLayer
 
     width, heads, kv, dim, ff = KELASUN_SIZES[size]
     q_rank, kv_rank = KELASUN_LATENTS[size]
-    unit = ff // (KELASUN_TOP + 1)            # the chosen experts and the shared one together are as wide as the dense ff
+    unit = kelasun_expert_width(ff)           # the chosen experts and the shared one together are as wide as the dense ff
     experts = KelasunExperts(KELASUN_EXPERTS, KELASUN_TOP, unit, ff - KELASUN_TOP * unit)
     made = []
     for index in range(layers):
@@ -943,7 +948,7 @@ def kelasun_roofline(name: str, kind: str, size: str, tokens: int, context: int,
     width, heads, kv, dim, ff = KELASUN_SIZES[size]
     q_rank, kv_rank = KELASUN_LATENTS[size]
     row, rot = kv_rank + KELASUN_ROT, KELASUN_ROT
-    unit = ff // (KELASUN_TOP + 1)
+    unit = kelasun_expert_width(ff)
     columns = KELASUN_EXPERTS * unit + (ff - KELASUN_TOP * unit)
     pairs = tokens * (tokens + 1) // 2 if context == tokens else tokens * context
     bytes_, flops = 0.0, 0.0

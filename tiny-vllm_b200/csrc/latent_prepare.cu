@@ -339,6 +339,27 @@ __global__ void heads_place_kernel(const T* __restrict__ src, T* dst, int64_t ds
     dst[token * dst_token_stride + head * dst_head_stride + j] = from_float<T>(v);
 }
 
+// bfloat16 with n, the strides and the addresses multiples of eight elements: eight values a thread and access
+__global__ void heads_place_bf16x8_kernel(const bf16* __restrict__ src, bf16* dst, int64_t dst_token_stride,
+                                          int64_t dst_head_stride, const bf16* gate, int64_t gate_token_stride,
+                                          int tokens, int heads, int n) {
+    const int64_t index = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int words = n / 8;
+    if (index >= (int64_t)tokens * heads * words) return;
+    const int j = (int)(index % words) * 8;
+    const int head = (int)((index / words) % heads);
+    const int64_t token = index / ((int64_t)words * heads);
+    float v[8];
+    unpack_bf16x8(ld_global_16(src + ((int64_t)head * tokens + token) * n + j), v);
+    if (gate) {
+        float g[8];
+        unpack_bf16x8(ld_global_16(gate + token * gate_token_stride + (int64_t)head * n + j), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g[i]))));
+    }
+    *reinterpret_cast<uint4*>(dst + token * dst_token_stride + head * dst_head_stride + j) = pack_bf16x8(v);
+}
+
 extern "C" int tvb_heads_place(const void* src, void* dst, long long dst_token_stride, long long dst_head_stride,
                                const void* gate, long long gate_token_stride, int tokens, int heads, int n, int dtype,
                                void* stream) {
@@ -351,6 +372,12 @@ extern "C" int tvb_heads_place(const void* src, void* dst, long long dst_token_s
     if (dtype == TVB_F32)
         heads_place_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)src, (float*)dst, dst_token_stride,
                                                                   dst_head_stride, (const float*)gate, gate_token_stride, tokens, heads, n);
+    else if (dtype == TVB_BF16 && n % 8 == 0 && dst_token_stride % 8 == 0 && dst_head_stride % 8 == 0 &&
+             (uintptr_t)src % 16 == 0 && (uintptr_t)dst % 16 == 0 &&
+             (!gate || (gate_token_stride % 8 == 0 && (uintptr_t)gate % 16 == 0)))
+        heads_place_bf16x8_kernel<<<(unsigned)((count / 8 + 255) / 256), 256, 0, s>>>(
+            (const bf16*)src, (bf16*)dst, dst_token_stride, dst_head_stride, (const bf16*)gate, gate_token_stride,
+            tokens, heads, n);
     else if (dtype == TVB_BF16)
         heads_place_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)src, (bf16*)dst, dst_token_stride,
                                                                  dst_head_stride, (const bf16*)gate, gate_token_stride, tokens, heads, n);

@@ -21,7 +21,7 @@ template <int ACT> __device__ __forceinline__ float expert_act(float z) {
     return __fdiv_rn(z, __fadd_rn(1.0f, expf(-z)));
 }
 
-template <typename T, int ACT>
+template <typename T, int ACT, bool WIDE>
 __global__ void route_act_kernel(const float* __restrict__ logits, int64_t logits_stride, const T* up,
                                  int64_t up_stride, T* __restrict__ out, int64_t out_stride,
                                  float* __restrict__ weights_out, int experts, int top, int ff, int shared_ff) {
@@ -64,11 +64,28 @@ __global__ void route_act_kernel(const float* __restrict__ logits, int64_t logit
     T* dst = out + token * out_stride;
     const int routed = experts * ff;
     // grid.y shares the columns: every block finds the token's experts for itself (a few dozen logits)
-    const int per_block = (routed + shared_ff + gridDim.y - 1) / gridDim.y;
+    int per_block = (routed + shared_ff + gridDim.y - 1) / gridDim.y;
+    if (WIDE) per_block = (per_block + 7) / 8 * 8;
     const int begin = blockIdx.y * per_block, end = min(routed + shared_ff, begin + per_block);
-    for (int c = begin + threadIdx.x; c < end; c += blockDim.x) {
-        const float a = expert_act<ACT>(to_float<T>(src[c]));
-        dst[c] = from_float<T>(c < routed ? __fmul_rn(a, share[c / ff]) : a);
+    if constexpr (WIDE) {
+        // bfloat16 rows whose pieces are whole 16-byte words: eight columns a thread and access (an expert's
+        // columns are a multiple of eight, so a word never straddles two experts)
+        for (int c = begin + threadIdx.x * 8; c < end; c += blockDim.x * 8) {
+            float v[8], o[8];
+            unpack_bf16x8(ld_global_16(src + c), v);
+            const float weight = c < routed ? share[c / ff] : 1.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float a = expert_act<ACT>(v[i]);
+                o[i] = c < routed ? __fmul_rn(a, weight) : a;
+            }
+            *reinterpret_cast<uint4*>(dst + c) = pack_bf16x8(o);
+        }
+    } else {
+        for (int c = begin + threadIdx.x; c < end; c += blockDim.x) {
+            const float a = expert_act<ACT>(to_float<T>(src[c]));
+            dst[c] = from_float<T>(c < routed ? __fmul_rn(a, share[c / ff]) : a);
+        }
     }
 }
 
@@ -90,12 +107,14 @@ extern "C" int tvb_route_act(const float* logits, long long logits_stride, const
     if (split > most) split = most;
     if (split > 65535) split = 65535;
     const dim3 grid(tokens, (unsigned)split);
-#define GO(T, ACT) route_act_kernel<T, ACT><<<grid, threads, 0, s>>>(                                      \
+    const bool wide = dtype == TVB_BF16 && ff % 8 == 0 && shared_ff % 8 == 0 && up_stride % 8 == 0 &&
+                      out_stride % 8 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)out % 16 == 0;
+#define GO(T, ACT, WIDE) route_act_kernel<T, ACT, WIDE><<<grid, threads, 0, s>>>(                          \
         logits, logits_stride, (const T*)up, up_stride, (T*)out, out_stride, weights_out, experts, top, ff, shared_ff)
-    if (dtype == TVB_F32 && act == TVB_ACT_RELU2) GO(float, TVB_ACT_RELU2);
-    else if (dtype == TVB_F32) GO(float, TVB_ACT_SILU_PLAIN);
-    else if (dtype == TVB_BF16 && act == TVB_ACT_RELU2) GO(bf16, TVB_ACT_RELU2);
-    else if (dtype == TVB_BF16) GO(bf16, TVB_ACT_SILU_PLAIN);
+    if (dtype == TVB_F32 && act == TVB_ACT_RELU2) GO(float, TVB_ACT_RELU2, false);
+    else if (dtype == TVB_F32) GO(float, TVB_ACT_SILU_PLAIN, false);
+    else if (dtype == TVB_BF16 && act == TVB_ACT_RELU2) { if (wide) GO(bf16, TVB_ACT_RELU2, true); else GO(bf16, TVB_ACT_RELU2, false); }
+    else if (dtype == TVB_BF16) { if (wide) GO(bf16, TVB_ACT_SILU_PLAIN, true); else GO(bf16, TVB_ACT_SILU_PLAIN, false); }
     else return TVB_BAD_ARGUMENT;
 #undef GO
     return tvb_last_error();
