@@ -69,11 +69,12 @@ def test_layer_norm_behind_the_residual_sum(width, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-def test_norm_over_whole_projections_and_query_temperature(dtype):
+@pytest.mark.parametrize("q_cols,k_cols,extra,kd,vd", [(44, 18, 7, 9, 3), (64, 32, 24, 16, 8), (1024, 256, 64, 128, 32)])
+def test_norm_over_whole_projections_and_query_temperature(q_cols, k_cols, extra, kd, vd, dtype):
+    """Sizes that fit no 16-byte access, and sizes that do (the kernel then moves eight values at a time)."""
     from tinyvllm_b200.ops import kernels
 
     g = torch.Generator().manual_seed(5)
-    q_cols, k_cols, extra = 44, 18, 7
     proj = (torch.randn(6, q_cols + k_cols + extra, generator=g) * 2).to(dtype)
     qw = (1 + 0.3 * torch.randn(q_cols, generator=g)).to(dtype)
     kw = (1 + 0.3 * torch.randn(k_cols, generator=g)).to(dtype)
@@ -90,10 +91,10 @@ def test_norm_over_whole_projections_and_query_temperature(dtype):
                             torch.tensor(positions, dtype=torch.int32, device=CUDA), 1e-5, temperature=(coef, every))
     close(dev, want, dtype)
     assert torch.equal(dev[:, q_cols + k_cols:].cpu(), proj[:, q_cols + k_cols:])          # the rest is untouched
-    # the same launch may store: the second segment as 2 kv heads of 9 keys, and 2 x 3 values from the rest
+    # the same launch may store: the second segment as 2 kv heads of keys, and 2 heads of values from the rest
     page, pages = 4, 4
-    key_cache = torch.full((pages, 2, page, 9), float("nan"), dtype=dtype, device=CUDA)
-    value_cache = torch.full((pages, 2, page, 3), float("nan"), dtype=dtype, device=CUDA)
+    key_cache = torch.full((pages, 2, page, kd), float("nan"), dtype=dtype, device=CUDA)
+    value_cache = torch.full((pages, 2, page, vd), float("nan"), dtype=dtype, device=CUDA)
     slots = [5, 0, 15, 9, -1, 2]
     again = proj.to(CUDA)
     kernels.projection_norm(again, [(0, q_cols, qw.to(CUDA), True), (q_cols, k_cols, kw.to(CUDA), False)],
@@ -105,10 +106,10 @@ def test_norm_over_whole_projections_and_query_temperature(dtype):
         if slot < 0:
             continue
         for head in range(2):
-            assert torch.equal(key_cache[slot // page, head, slot % page], dev[t, q_cols + 9 * head:q_cols + 9 * head + 9])
+            assert torch.equal(key_cache[slot // page, head, slot % page], dev[t, q_cols + kd * head:q_cols + kd * head + kd])
             assert torch.equal(value_cache[slot // page, head, slot % page],
-                               proj[t, q_cols + k_cols + 3 * head:q_cols + k_cols + 3 * head + 3].to(CUDA))
-    assert torch.isnan(key_cache.float()).sum().item() == (pages * page - 5) * 2 * 9      # no other row was touched
+                               proj[t, q_cols + k_cols + vd * head:q_cols + k_cols + vd * head + vd].to(CUDA))
+    assert torch.isnan(key_cache.float()).sum().item() == (pages * page - 5) * 2 * kd      # no other row was touched
     # positions 8 and 9 lie on the two sides of a period's edge: (p + 1) / every is 0 and then 1
     ratio = (dev[2, :q_cols].double() / want[2, :q_cols].cuda()).mean().item()
     assert ratio == pytest.approx(1.0, abs=2e-2)

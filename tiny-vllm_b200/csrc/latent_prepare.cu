@@ -35,18 +35,35 @@ struct CacheRows {
     int num_kv, key_dim, value_dim, page_size, v_at;
 };
 
-template <typename T, typename W>
+// The row waits in shared memory as float32 between the statistic and the result, so global memory is read
+// once; WIDE: bfloat16 with every offset, size and stride a multiple of eight elements, eight values a thread
+// and access.
+template <typename T, typename W, bool WIDE>
 __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment first, NormSegment second,
                                        const int* __restrict__ positions, float eps, float coef, int every,
                                        CacheRows rows) {
+    extern __shared__ float row_values[];
     __shared__ float scratch[32];
     const NormSegment seg = blockIdx.y == 0 ? first : second;
     T* row = proj + (int64_t)blockIdx.x * stride + seg.at;
     const W* weight = (const W*)seg.weight;
     float part = 0.0f;
-    for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
-        const float v = to_float<T>(row[i]);
-        part = __fmaf_rn(v, v, part);
+    if constexpr (WIDE) {
+        for (int i = threadIdx.x * 8; i < seg.cols; i += blockDim.x * 8) {
+            float v[8];
+            unpack_bf16x8(ld_global_16(row + i), v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                row_values[i + e] = v[e];
+                part = __fmaf_rn(v[e], v[e], part);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
+            const float v = to_float<T>(row[i]);
+            row_values[i] = v;
+            part = __fmaf_rn(v, v, part);
+        }
     }
     const float total = block_sum(part, scratch);
     const float inverse = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)seg.cols), eps)));
@@ -59,21 +76,49 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
     const int slot = (blockIdx.y == 1 && rows.slots) ? rows.slots[blockIdx.x] : -1;
     const int64_t page_row = slot >= 0 ? (int64_t)(slot / rows.page_size) * rows.num_kv : 0;
     const int offset = slot >= 0 ? slot % rows.page_size : 0;
-    for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
-        float o = __fmul_rn(__fmul_rn(to_float<T>(row[i]), inverse), to_float<W>(weight[i]));
-        if (seg.tempered) o = __fmul_rn(o, temperature);
-        const T rounded = from_float<T>(o);
-        row[i] = rounded;
-        if (slot >= 0) {
-            const int head = i / rows.key_dim, dim = i % rows.key_dim;
-            ((T*)rows.key_cache)[((page_row + head) * rows.page_size + offset) * rows.key_dim + dim] = rounded;
+    if constexpr (WIDE) {
+        for (int i = threadIdx.x * 8; i < seg.cols; i += blockDim.x * 8) {
+            float w[8], o[8];
+            unpack_bf16x8(ld_global_16(weight + i), w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                o[e] = __fmul_rn(__fmul_rn(row_values[i + e], inverse), w[e]);
+                if (seg.tempered) o[e] = __fmul_rn(o[e], temperature);
+            }
+            const uint4 packed = pack_bf16x8(o);
+            *reinterpret_cast<uint4*>(row + i) = packed;
+            if (slot >= 0) {
+                const int head = i / rows.key_dim, dim = i % rows.key_dim;      // key_dim is a multiple of eight
+                *reinterpret_cast<uint4*>((bf16*)rows.key_cache +
+                                          ((page_row + head) * rows.page_size + offset) * rows.key_dim + dim) = packed;
+            }
         }
-    }
-    if (slot >= 0) {
-        const T* values = proj + (int64_t)blockIdx.x * stride + rows.v_at;
-        for (int i = threadIdx.x; i < rows.num_kv * rows.value_dim; i += blockDim.x) {
-            const int head = i / rows.value_dim, dim = i % rows.value_dim;
-            ((T*)rows.value_cache)[((page_row + head) * rows.page_size + offset) * rows.value_dim + dim] = values[i];
+        if (slot >= 0) {
+            const bf16* values = proj + (int64_t)blockIdx.x * stride + rows.v_at;
+            for (int i = threadIdx.x * 8; i < rows.num_kv * rows.value_dim; i += blockDim.x * 8) {
+                const int head = i / rows.value_dim, dim = i % rows.value_dim;
+                *reinterpret_cast<uint4*>((bf16*)rows.value_cache +
+                                          ((page_row + head) * rows.page_size + offset) * rows.value_dim + dim) =
+                    ld_global_16(values + i);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
+            float o = __fmul_rn(__fmul_rn(row_values[i], inverse), to_float<W>(weight[i]));
+            if (seg.tempered) o = __fmul_rn(o, temperature);
+            const T rounded = from_float<T>(o);
+            row[i] = rounded;
+            if (slot >= 0) {
+                const int head = i / rows.key_dim, dim = i % rows.key_dim;
+                ((T*)rows.key_cache)[((page_row + head) * rows.page_size + offset) * rows.key_dim + dim] = rounded;
+            }
+        }
+        if (slot >= 0) {
+            const T* values = proj + (int64_t)blockIdx.x * stride + rows.v_at;
+            for (int i = threadIdx.x; i < rows.num_kv * rows.value_dim; i += blockDim.x) {
+                const int head = i / rows.value_dim, dim = i % rows.value_dim;
+                ((T*)rows.value_cache)[((page_row + head) * rows.page_size + offset) * rows.value_dim + dim] = values[i];
+            }
         }
     }
 }
@@ -99,18 +144,34 @@ extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first
     NormSegment first{first_at, first_cols, first_weight, first_tempered};
     NormSegment second{second_at, second_cols, second_weight, second_tempered};
     const int widest = first_cols > second_cols ? first_cols : second_cols;
-    const int threads = widest >= 2048 ? 512 : (widest >= 512 ? 256 : 128);
+    const size_t smem = (size_t)widest * sizeof(float);
+    if (smem > 200 * 1024) return TVB_BAD_ARGUMENT;
+    const bool wide = dtype == TVB_BF16 && weight_dtype == TVB_BF16 && (uintptr_t)proj % 16 == 0 && stride % 8 == 0 &&
+                      first_at % 8 == 0 && first_cols % 8 == 0 && second_at % 8 == 0 && second_cols % 8 == 0 &&
+                      (uintptr_t)first_weight % 16 == 0 && (!second_weight || (uintptr_t)second_weight % 16 == 0) &&
+                      (!slots || (key_dim % 8 == 0 && value_dim % 8 == 0 && v_at % 8 == 0 &&
+                                  (uintptr_t)key_cache % 16 == 0 && (uintptr_t)value_cache % 16 == 0));
+    const int per_thread = wide ? 8 : 1;
+    const int threads = widest / per_thread >= 512 ? 512 : (widest / per_thread >= 256 ? 256 : 128);
     for (int start = 0; start < tokens; start += 65535) {      // grid.x carries the tokens
         const int count = tokens - start < 65535 ? tokens - start : 65535;
         dim3 grid(count, second_cols > 0 ? 2 : 1);
         const int* p = positions ? positions + start : nullptr;
         CacheRows part = rows;
         if (part.slots) part.slots += start;
-#define GO(T, W) projection_norm_kernel<T, W><<<grid, threads, 0, s>>>((T*)proj + (int64_t)start * stride, stride, \
-                                                                        first, second, p, eps, coef, every, part)
-        if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float);
-        else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) GO(bf16, bf16);
-        else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float);
+#define GO(T, W, WIDE)                                                                                         \
+    do {                                                                                                       \
+        auto kernel = projection_norm_kernel<T, W, WIDE>;                                                      \
+        if (smem > 48 * 1024) {                                                                                \
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                               \
+        }                                                                                                      \
+        kernel<<<grid, threads, smem, s>>>((T*)proj + (int64_t)start * stride, stride, first, second, p, eps,  \
+                                           coef, every, part);                                                 \
+    } while (0)
+        if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float, false);
+        else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) { if (wide) GO(bf16, bf16, true); else GO(bf16, bf16, false); }
+        else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float, false);
         else return TVB_BAD_ARGUMENT;
 #undef GO
     }
