@@ -923,12 +923,12 @@ def kelasun_config(size: str, layers: int):
     for index in range(layers):
         if index % 2 == 0:
             made.append(KelasunLayer(type="attention", heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
-                                     q_temp=(0.5, 256), mlp=experts))
+                                     q_temp=(0.4, 512), mlp=experts))
         else:
             made.append(KelasunLayer(type="latent_attention", heads=heads, dim=dim // 2, vdim=dim, scale=dim ** -0.5,
-                                     q_rank=q_rank, kv_rank=kv_rank, rot_dim=KELASUN_ROT, rot_base=250000.0,
-                                     rot_scaling=(4.0, 2048.0, 32.0, 1.0), mlp=experts))
-    return KelasunConfig(vocab=MODEL["vocab_size"], width=width, norm_eps=1e-5, postln_alpha=2.5, logit_scale=1.0,
+                                     q_rank=q_rank, kv_rank=kv_rank, rot_dim=KELASUN_ROT, rot_base=1000000.0,
+                                     rot_scaling=(8.0, 4096.0, 32.0, 1.0), mlp=experts))
+    return KelasunConfig(vocab=MODEL["vocab_size"], width=width, norm_eps=1e-6, postln_alpha=2.0, logit_scale=1.0,
                          layers=tuple(made))
 
 

@@ -50,7 +50,7 @@ KELASUN_CONFIGS = {
     # a cached row wider than 256 elements (the wide form of the row kernel), no rotated part in one
     # layer, four of sixteen experts
     "c": KelasunConfig(vocab=130, width=128, norm_eps=1e-6, postln_alpha=3.0, logit_scale=1.0, layers=(
-        _l(2, 32, 64, 32, 64, 256, 250000.0, (4.0, 128.0, 32.0, 1.0), KelasunExperts(16, 4, 16, 16)),
+        _l(2, 32, 64, 32, 64, 256, 200000.0, (3.0, 128.0, 16.0, 1.0), KelasunExperts(16, 4, 16, 16)),
         _a(8, 8, 32, 16, (0.7, 64), KelasunExperts(16, 4, 16, 16)),
         _l(2, 32, 0, 32, 64, 96, None, None, None))),
     # sizes that fit no vector access at all: a width and a vocabulary that are no multiples of four, odd head

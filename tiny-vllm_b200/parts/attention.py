@@ -127,8 +127,9 @@ class WindowedAttention(Part):
                  sink: bool = False, float32_output: bool = False) -> None:
         if num_heads % num_kv_heads:
             raise ValueError("query heads must be a multiple of key-value heads")
-        if not 0 < key_dim <= 256 or not 0 < value_dim <= 256:
-            raise ValueError(f"the attention kernels take key and value sizes up to 256, not {key_dim} / {value_dim}")
+        limit = kernels.ATTENTION_ROWS_MAX_DIM
+        if not 0 < key_dim <= limit or not 0 < value_dim <= limit:
+            raise ValueError(f"the attention kernels take key and value sizes up to {limit}, not {key_dim} / {value_dim}")
         if qk_norm not in (None, "unit", "weight", "whole"):
             raise ValueError(f"qk_norm is None, 'unit', 'weight' or 'whole', not {qk_norm!r}")
         if gate not in (False, True, "head"):
