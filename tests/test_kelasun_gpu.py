@@ -110,6 +110,12 @@ def test_norm_over_whole_projections_and_query_temperature(q_cols, k_cols, extra
             assert torch.equal(value_cache[slot // page, head, slot % page],
                                proj[t, q_cols + k_cols + vd * head:q_cols + k_cols + vd * head + vd].to(CUDA))
     assert torch.isnan(key_cache.float()).sum().item() == (pages * page - 5) * 2 * kd      # no other row was touched
+    if dtype == torch.bfloat16:
+        # norm weights that a checkpoint stores in 32-bit stay so: the same values give the same result
+        wide = proj.to(CUDA)
+        kernels.projection_norm(wide, [(0, q_cols, qw.float().to(CUDA), True), (q_cols, k_cols, kw.float().to(CUDA), False)],
+                                torch.tensor(positions, dtype=torch.int32, device=CUDA), 1e-5, temperature=(coef, every))
+        assert torch.equal(wide, dev)
     # positions 8 and 9 lie on the two sides of a period's edge: (p + 1) / every is 0 and then 1
     ratio = (dev[2, :q_cols].double() / want[2, :q_cols].cuda()).mean().item()
     assert ratio == pytest.approx(1.0, abs=2e-2)

@@ -35,6 +35,16 @@ struct CacheRows {
     int num_kv, key_dim, value_dim, page_size, v_at;
 };
 
+// eight consecutive weights (16-byte aligned) as float32
+template <typename W> __device__ __forceinline__ void load_weights8(const W* p, float* w);
+template <> __device__ __forceinline__ void load_weights8<bf16>(const bf16* p, float* w) {
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(p), w);
+}
+template <> __device__ __forceinline__ void load_weights8<float>(const float* p, float* w) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+}
+
 // The row waits in shared memory as float32 between the statistic and the result, so global memory is read
 // once; WIDE: bfloat16 with every offset, size and stride a multiple of eight elements, eight values a thread
 // and access.
@@ -79,7 +89,7 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
     if constexpr (WIDE) {
         for (int i = threadIdx.x * 8; i < seg.cols; i += blockDim.x * 8) {
             float w[8], o[8];
-            unpack_bf16x8(ld_global_16(weight + i), w);
+            load_weights8<W>(weight + i, w);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 o[e] = __fmul_rn(__fmul_rn(row_values[i + e], inverse), w[e]);
@@ -146,7 +156,7 @@ extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first
     const int widest = first_cols > second_cols ? first_cols : second_cols;
     const size_t smem = (size_t)widest * sizeof(float);
     if (smem > 200 * 1024) return TVB_BAD_ARGUMENT;
-    const bool wide = dtype == TVB_BF16 && weight_dtype == TVB_BF16 && (uintptr_t)proj % 16 == 0 && stride % 8 == 0 &&
+    const bool wide = dtype == TVB_BF16 && (uintptr_t)proj % 16 == 0 && stride % 8 == 0 &&
                       first_at % 8 == 0 && first_cols % 8 == 0 && second_at % 8 == 0 && second_cols % 8 == 0 &&
                       (uintptr_t)first_weight % 16 == 0 && (!second_weight || (uintptr_t)second_weight % 16 == 0) &&
                       (!slots || (key_dim % 8 == 0 && value_dim % 8 == 0 && v_at % 8 == 0 &&
@@ -171,7 +181,7 @@ extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first
     } while (0)
         if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float, false);
         else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) { if (wide) GO(bf16, bf16, true); else GO(bf16, bf16, false); }
-        else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float, false);
+        else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) { if (wide) GO(bf16, float, true); else GO(bf16, float, false); }
         else return TVB_BAD_ARGUMENT;
 #undef GO
     }
