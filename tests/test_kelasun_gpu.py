@@ -523,6 +523,31 @@ def test_bfloat16_generation_through_the_engine(folders):
             assert output.output_token_ids[0] == int(logits.argmax())
 
 
+def test_bfloat16_steps_run_on_the_tensor_core_kernels(folders, monkeypatch):
+    """Sizes in steps of 16: prompt portions of both mixers go to the tile kernel, decoded tokens to the
+    kernel for single tokens, none to the row kernel; the latent layers hand over no value cache."""
+    from tinyvllm_b200.ops import kernels
+
+    seen = {"attention_tiles": [], "attention_tiles_singles": [], "attention_rows": []}
+    for fn in seen:
+        original = getattr(kernels, fn)
+
+        def watched(*args, _original=original, _fn=fn, **kwargs):
+            seen[_fn].append(args[2] is None)          # the value cache
+            return _original(*args, **kwargs)
+        monkeypatch.setattr(kernels, fn, watched)
+    name = "c"
+    requests = {"t": tokens_of(KELASUN_CONFIGS[name].vocab, 90, 31)}
+    runner = make_runner(folders[name], torch.bfloat16, 16, 16)
+    with torch.inference_mode():
+        rh.run_steps(runner, rh.tail_by_one(requests, 3))
+    layers = [layer.type for layer in KELASUN_CONFIGS[name].layers]
+    latent = [kind == "latent_attention" for kind in layers]
+    assert seen["attention_tiles"] == latent                      # one prompt step
+    assert seen["attention_tiles_singles"] == latent * 3          # three decoded tokens
+    assert not seen["attention_rows"]
+
+
 def test_command_line(folders, capsys):
     """python -m tinyvllm_b200 on a Kelasun folder: greedy tokens of the plain implementation, also
     streamed, and with weights drawn from a seed instead of the file."""
