@@ -175,7 +175,7 @@ __device__ __forceinline__ float gate_of(float g) { return __fdiv_rn(1.0f, __fad
 
 // What the rows of one launch share beyond the sizes: `slopes` (one float a query head, or null):
 // slope * (position - j) is taken off the score of key j; `sinks` (one float a query head, or null):
-// exp(sink) joins the softmax's denominator once, with no key and no value; `gate_per_head`: the
+// exp(sink) is added to the softmax's denominator and to nothing else (nothing is attended for it); `gate_per_head`: the
 // gate holds one number a head instead of one a value.
 struct RowExtras {
     const float* slopes;

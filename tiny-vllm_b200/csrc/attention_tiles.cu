@@ -3,8 +3,8 @@
 // values TILES_VALUE_DIM wide (both multiples of 16; the library is compiled per pair), a
 // sliding window that may keep the first `keep_first` keys visible, an optional output gate (one number
 // a value, or one a head), an optional distance bias (head h takes slopes[h] * (p - j) off the score of
-// key j) and an optional sink a head (exp(sink) joins the softmax's denominator once, with no key and no
-// value).  Compiled with TILES_VALUE_IN_KEY=1 the values are the first TILES_VALUE_DIM elements of the
+// key j) and an optional sink a head (exp(sink) is added to the softmax's denominator and to nothing
+// else).  Compiled with TILES_VALUE_IN_KEY=1 the values are the first TILES_VALUE_DIM elements of the
 // key rows themselves (attention over latents that serve as keys and values): no value cache is read
 // and the key tile in shared memory is the value tile too.
 //

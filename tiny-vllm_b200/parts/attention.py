@@ -110,7 +110,7 @@ class WindowedAttention(Part):
     ``query_temperature`` (coef, every): q at position p is multiplied by 1 + coef * ln(floor((p + 1) /
     every) + 1).  ``distance_slope_exponent`` = c: head h takes 2^(-c (h + 1) / heads) * (i - j) off
     the score of key j for query i.  ``sink``: a learned number a head (tensor ``sink``) whose
-    exponential joins the softmax's denominator once, with no key and no value.  ``gate="head"``:
+    exponential is added to the softmax's denominator and to nothing else.  ``gate="head"``:
     the gate is one number a head, sigmoid(W_g x)_h with W_g [heads, width].  ``float32_output``: the
     output projection leaves its float32 sums unrounded (for a float32 residual sum).
 

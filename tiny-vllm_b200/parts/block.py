@@ -116,7 +116,7 @@ class ParallelResidualBlock(Block):
 
 
 class PostNormResidualBlock(Block):
-    """Norm after the sum: x <- norm1(alpha * x + mixer(x)), then x <- norm2(alpha * x +
+    """The norm follows the residual sum: x <- norm1(alpha * x + mixer(x)), then x <- norm2(alpha * x +
     feed_forward(x)); both sublayers read x itself.  A layer may have no feed-forward: it then has no
     second step, unless its checkpoint holds the second norm, which is then applied to alpha * x.  The stream x is float32 whatever the storage type; the norms hand on, beside it,
     its one rounding to the storage type (``stream.rounded``), which is what the next products read.
